@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""LayerAdam throughput benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            # the CUDA path
+    python bench.py --impl reference [--gpus N] [--steps K] [--warmup W]   # the reference's CPU kernel
+
+A step is one LayerAdam update of one Llama-3.1-8B decoder layer flattened to 218,112,000
+fp32 parameters (bf16 gradient in, fp32 p / m / v updated in place, bf16 copy out): 28
+algorithmic bytes per parameter.  Synthetic data with the layer's value distributions.
+
+N = 1   state resident in HBM, one launch per step.
+N > 1   launched by torchrun, one rank per GPU: each rank brings its own full-layer bf16
+        gradient, owns 1/N of p / m / v, the gradients are averaged in fp32 in rank order
+        (fused peer reads, or NCCL reduce-scatter with --dp-mode nccl), the shard is updated
+        and the bf16 shards are all-gathered.  The layer size is fixed, so scaling is strong.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+N_LAYER = 218_112_000  # q/o 4096x4096, k/v 4096x1024, gate/up/down 4096x14336, two 4096 norms
+BYTES_PER_PARAM = 28   # read p4 + g2 + m4 + v4, write p4 + m4 + v4 + bf16 2
+HP = dict(lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+WORKLOAD = "llama3.1-8b decoder layer, flat n=218112000, fp32 p/m/v + bf16 grad -> bf16 copy"
+METRIC = "LayerAdam Gparams/s"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch at n = 218,112,000, scaled by n
+# from the ncu capture summarised in profiles/ (bytes per parameter); None until captured.
+NCU_TRAFFIC_BYTES_PER_PARAM = None
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks: read-only NVML sampling in a thread while the GPU is under load
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, torch_index: int, period_s: float = 0.004):
+        self.samples = []  # (t, sm_mhz, reasons_mask, in_timed_region)
+        self.period = period_s
+        self.in_region = False
+        self._stop = threading.Event()
+        self.ok = False
+        self.sm_max = None
+        try:
+            import pynvml
+            import torch
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(torch_index).uuid)
+            h = None
+            for i in range(pynvml.nvmlDeviceGetCount()):
+                hi = pynvml.nvmlDeviceGetHandleByIndex(i)
+                u = pynvml.nvmlDeviceGetUUID(hi)
+                u = u.decode() if isinstance(u, bytes) else u
+                if uuid in u:
+                    h = hi
+                    break
+            self.h = h if h is not None else pynvml.nvmlDeviceGetHandleByIndex(torch_index)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception as exc:  # NVML not reachable: report that instead of clocks
+            self.err = repr(exc)
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _read(self):
+        nv = self.nv
+        sm = int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+        try:
+            mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+        except Exception:
+            mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+        return sm, mask
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                sm, mask = self._read()
+                self.samples.append((time.perf_counter(), sm, mask, self.in_region))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.ok:
+            self.thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self.ok and self.thread.is_alive():
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "NVML unavailable: " + getattr(self, "err", "")}
+        timed = [s for s in self.samples if s[3]]
+        used, scope = (timed, "timed region") if len(timed) >= 3 else ([s for s in self.samples], "whole loaded run (timed region too short to sample)")
+        if not used:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "note": "no samples"}
+        mask = 0
+        for s in used:
+            mask |= s[2]
+        reasons = [name for bit, name in self.REASONS.items() if mask & bit and name != "gpu_idle"]
+        return {"sm_mhz": statistics.median(s[1] for s in used), "sm_max_mhz": self.sm_max, "reasons": reasons,
+                "samples": len(used), "scope": scope}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arms (the reference's kernel when its prebuilt module is present, else the C port)
+# ---------------------------------------------------------------------------------------------
+def cpu_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_cpu_arm(n: int, steps: int, warmup: int, budget_s: float):
+    """Time the CPU LayerAdam step on this host with all usable threads.
+    Returns dict(value=Gparams/s, kind, cores, sample, ms_per_step, steps)."""
+    import numpy as np
+    import torch
+    threads = cpu_threads()
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    torch.set_num_threads(threads)
+    from oracle import build_ref
+    ref = build_ref.load()
+    gen = torch.Generator().manual_seed(0)
+    p = torch.empty(n).normal_(0, 0.02, generator=gen)
+    p[-8192:] = 1.0
+    m, v = torch.zeros(n), torch.zeros(n)
+    grads = [torch.empty(n).normal_(0, 1e-3, generator=gen).to(torch.bfloat16) for _ in range(2)]
+    lr, (b1, b2), eps, wd = HP["lr"], HP["betas"], HP["eps"], HP["weight_decay"]
+    if ref is not None:
+        kind = "reference"
+        ref.create_adam(0, lr, b1, b2, eps, wd, True, False)
+
+        def one(step):
+            ref.adam_update(0, step, lr, b1, b2, eps, wd, True, p, grads[step & 1], m, v)
+    else:
+        kind = "port"
+        from oracle import oracle as O
+        opt = O.OracleAdam(lr, b1, b2, eps, wd, True)
+        pn, mn, vn = p.numpy(), m.numpy(), v.numpy()
+        gn = [g.view(torch.int16).numpy().view(np.uint16) for g in grads]
+
+        def one(step):
+            opt.adam_update(step, lr, b1, b2, eps, wd, True, pn, gn[step & 1], mn, vn)
+    step = 0
+    t_w0 = time.perf_counter()
+    for _ in range(max(1, warmup)):
+        step += 1
+        one(step)
+    per = (time.perf_counter() - t_w0) / max(1, warmup)
+    steps = max(1, min(steps, int(budget_s / max(per, 1e-6))))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step += 1
+        one(step)
+    dt = time.perf_counter() - t0
+    # the reference converts fp32 -> bf16 in a separate CPU pass before the upload
+    # (transformer_layer.py:296-305); time it too, it is part of what the fused kernel replaces
+    stage = torch.empty(n, dtype=torch.bfloat16)
+    t1 = time.perf_counter()
+    for _ in range(2):
+        stage.copy_(p)
+    cast_ms = (time.perf_counter() - t1) / 2 * 1e3
+    return dict(value=n * steps / dt / 1e9, unit="Gparams/s", cores=threads, kind=kind,
+                sample=f"{steps} full-layer steps (n={n}) after {max(1, warmup)} warm-up, bf16 grad, all host threads; "
+                       f"separate fp32->bf16 cast pass {cast_ms:.1f} ms not included",
+                ms_per_step=dt / steps * 1e3, steps=steps, bf16_cast_ms=cast_ms)
+
+
+def main_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    r = run_cpu_arm(args.n, args.steps, args.warmup, budget_s=90.0)
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": "Gparams/s", "n_gpus": args.gpus,
+            "steps": r["steps"], "warmup": max(1, args.warmup), "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "where": "host CPU"},
+            "cpu_baseline": {"value": r["value"], "unit": "Gparams/s", "cores": r["cores"], "kind": r["kind"],
+                             "sample": r["sample"]},
+            "e2e": {"value": r["value"], "unit": "Gparams/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------
+# the CUDA arm
+# ---------------------------------------------------------------------------------------------
+def main_b200(args):
+    import torch
+    import torch.distributed as dist
+    from slideformer_b200 import LayerAdam, _lib
+    from slideformer_b200.host_io import HostGradStepper
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    n = args.n
+    K, W = args.steps, max(3, args.warmup)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    NG = 3  # rotating gradient buffers: a fresh gradient every step
+    extra = {}
+    if world == 1:
+        p = torch.empty(n, device=dev).normal_(0, 0.02, generator=gen)
+        p[-8192:] = 1.0
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        out = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        grads = [torch.empty(n, device=dev).normal_(0, 1e-3, generator=gen).to(torch.bfloat16) for _ in range(NG)]
+        opt = LayerAdam(**HP)
+        group = dict(opt.defaults, step=0)
+
+        def one_step(i):
+            group["step"] += 1
+            opt.step_chunk(p, grads[i % NG], m, v, group, out)
+        hbm_bytes_per_launch = BYTES_PER_PARAM * n
+        parallelism = "single GPU, state resident in HBM"
+        scaling = "strong"
+    else:
+        from slideformer_b200.shared_data_parallel import ShardedLayerAdam
+        sh = ShardedLayerAdam(numel=n, device=dev, mode=args.dp_mode, **HP)
+        sh.params_shard.normal_(0, 0.02, generator=gen)
+        for k in range(NG):
+            sh.grad_buffer(k).copy_(torch.empty(n, device=dev).normal_(0, 1e-3, generator=gen).to(torch.bfloat16))
+
+        def one_step(i):
+            sh.step(i % NG)
+        hbm_bytes_per_launch = BYTES_PER_PARAM * sh.shard_numel + 2 * sh.shard_numel * (world - 1 if args.dp_mode == "fused" else 0)
+        parallelism = f"dp{world}: state sharded 1/{world}, {sh.describe()}"
+        scaling = "strong"
+
+    # ---- warm-up, then the timed region: K steps, device-timed, max over ranks ----------------
+    for i in range(W):
+        one_step(i)
+    barrier()
+    launches0 = lib.sf_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.in_region = True
+    e0.record()
+    for i in range(K):
+        one_step(i)
+    e1.record()
+    barrier()
+    sampler.in_region = False
+    launches = lib.sf_launch_count() - launches0
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / K
+    value = n / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per-launch duration of the dominant kernel (roofline numerator) -----------------------
+    R = min(max(K, 10), 50)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(R)]
+    if world == 1:
+        for i in range(R):
+            evs[i][0].record()
+            one_step(i)
+            evs[i][1].record()
+        torch.cuda.synchronize()
+        kern_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    else:
+        kern_ms = sh.time_kernel_only(R)
+        extra.update(sh.breakdown(R))
+        barrier()
+    peak, which = measured_peak()
+    achieved = hbm_bytes_per_launch / (kern_ms * 1e-3) / 1e9
+    units = n if world == 1 else sh.shard_numel
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": (NCU_TRAFFIC_BYTES_PER_PARAM * units) if NCU_TRAFFIC_BYTES_PER_PARAM else None,
+                "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs, burst copy)" if which == "measured" else "fallback 6650 GB/s",
+                "kernel": "adam_vec4_kernel", "kernel_ms": kern_ms, "bytes_per_launch": hbm_bytes_per_launch,
+                "frac_of_nominal_8000": achieved / 8000.0}
+
+    # ---- end to end through the public API with host buffers -----------------------------------
+    e2e = None
+    if world == 1:
+        g_host = [grads[k].cpu().pin_memory() for k in range(2)]
+        out_host = torch.empty(n, dtype=torch.bfloat16).pin_memory()
+        stepper = HostGradStepper(opt, n, dev, chunk_numel=args.e2e_chunk)
+        E = max(3, min(K, 20))
+        for i in range(3):
+            group["step"] += 1
+            stepper.step(p, g_host[i & 1], m, v, out, out_host, group)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        a.record()
+        for i in range(E):
+            group["step"] += 1
+            stepper.step(p, g_host[i & 1], m, v, out, out_host, group)
+        b.record()
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        e2e_ms = max(a.elapsed_time(b), wall_ms) / E
+        e2e = {"value": n / (e2e_ms * 1e-3) / 1e9, "unit": "Gparams/s", "h2d_bytes_per_step": 2 * n,
+               "d2h_bytes_per_step": 2 * n, "ms_per_step": e2e_ms, "steps": E,
+               "path": "HostGradStepper: pinned bf16 gradient -> HBM-resident LayerAdam.step_chunk -> pinned bf16 weights, "
+                       f"{args.e2e_chunk}-element chunks on three streams"}
+        # fully host-resident state (p, m, v and g in pinned host memory) streamed through the GPU
+        if args.host_state:
+            ph, mh, vh = (torch.empty(n).pin_memory() for _ in range(3))
+            ph.copy_(p)
+            mh.zero_()
+            vh.zero_()
+            hopt = LayerAdam(**HP)
+            hg = dict(hopt.defaults, step=0)
+            for i in range(4):
+                if i == 1:
+                    torch.cuda.synchronize()
+                    t0 = time.perf_counter()
+                hg["step"] += 1
+                hopt.step_chunk(ph, g_host[i & 1], mh, vh, hg, out)
+            torch.cuda.synchronize()
+            hs_ms = (time.perf_counter() - t0) * 1e3 / 3
+            extra["e2e_host_state"] = {"value": n / (hs_ms * 1e-3) / 1e9, "unit": "Gparams/s", "ms_per_step": hs_ms,
+                                       "h2d_bytes_per_step": 14 * n, "d2h_bytes_per_step": 12 * n,
+                                       "h2d_gbs": 14 * n / (hs_ms * 1e-3) / 1e9, "d2h_gbs": 12 * n / (hs_ms * 1e-3) / 1e9,
+                                       "path": "sf_adam_update_host: p, m, v, g in pinned host memory, double-buffered chunks"}
+            del ph, mh, vh
+    else:
+        e2e = sh.e2e(args, K)
+    sampler.stop()
+
+    cpu_baseline = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        r = run_cpu_arm(n, 8, 2, budget_s=20.0)
+        cpu_baseline = {"value": r["value"], "unit": "Gparams/s", "cores": r["cores"], "kind": r["kind"],
+                        "sample": r["sample"], "ms_per_step": r["ms_per_step"], "bf16_cast_ms": r["bf16_cast_ms"]}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "Gparams/s", "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "parallelism": parallelism,
+                           "l2": "inputs (3.05 GB per step) exceed the 126 MB L2; gradient buffer rotates every step",
+                           "hyper": {"lr": HP["lr"], "betas": list(HP["betas"]), "eps": HP["eps"], "weight_decay": HP["weight_decay"]}},
+                "hbm_gbs": BYTES_PER_PARAM * value, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+                "gpu_launches": int(launches), "clocks": sampler.summary()}
+        line.update(extra)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--n", type=int, default=N_LAYER, help="flat layer size (parity and sweep runs only)")
+    ap.add_argument("--dp-mode", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--e2e-chunk", type=int, default=16 * 1024 * 1024)
+    ap.add_argument("--host-state", action="store_true", default=True)
+    ap.add_argument("--no-host-state", dest="host_state", action="store_false")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return main_reference(args)
+    return main_b200(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,175 @@
+/*
+ * C ABI of the B200 LayerAdam library (libslideformer_b200.so).
+ *
+ * The library replaces the CPU Adam extension of the reference project on its per-layer
+ * optimizer path.  The reference binds three functions through pybind11
+ * (optimizer/layer_adam/csrc/cpu_adam.cpp:8-13: create_adam, adam_update, destroy_adam) that
+ * take torch CPU tensors.  The entry points below take plain pointers and sizes instead, so
+ * any host language can bind them; the element buffers are DEVICE pointers (HBM) unless an
+ * entry point says otherwise.  bf16 values are raw uint16_t bit patterns.
+ *
+ * Conventions
+ *   - every function returns an SfStatus (0 = success); sf_last_error() gives the message of
+ *     the calling thread's last failure.  No C++ exception crosses this boundary.
+ *   - kernels are launched asynchronously on the CUDA stream the caller passes (a
+ *     cudaStream_t cast to void*; NULL = the legacy default stream).  The caller owns all
+ *     buffers and the library retains none of them after the work on the stream completes.
+ *   - there is no CPU implementation behind these calls: without a CUDA device they fail
+ *     with SF_ERR_CUDA.
+ */
+#ifndef SLIDEFORMER_B200_H
+#define SLIDEFORMER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SF_ABI_VERSION 1
+
+typedef enum SfStatus {
+    SF_OK = 0,
+    SF_ERR_NULL = 1,       /* a required pointer is NULL                                  */
+    SF_ERR_ALIGN = 2,      /* a pointer or size breaks an alignment rule the call states   */
+    SF_ERR_SIZE = 3,       /* n overflows, or a range / scratch size is inconsistent       */
+    SF_ERR_UNKNOWN_ID = 4, /* optimizer id was never created (the reference dereferences
+                              a null pointer here, cpu_adam_impl.cpp:239-240)             */
+    SF_ERR_CUDA = 5,       /* a CUDA runtime call failed; message holds cudaGetErrorString */
+    SF_ERR_DTYPE = 6,      /* unsupported gradient dtype code (reference: runtime_error,
+                              cpu_adam_impl.cpp:255-261)                                  */
+    SF_ERR_ARG = 7         /* any other invalid argument (world size, chunk size, ...)     */
+} SfStatus;
+
+/* Gradient element type.  Parameters, exp_avg and exp_avg_sq are always fp32: the triples
+ * <float, BFloat16, float> and <float, float, float> of cpu_adam_impl.cpp:187-188. */
+typedef enum SfGradDtype { SF_GRAD_BF16 = 0, SF_GRAD_F32 = 1 } SfGradDtype;
+
+/* The per-call constants of the element loop, all binary32, computed on the host exactly as
+ * Adam_Optimizer::Step_AVX derives them (cpu_adam.h:124-150). */
+typedef struct SfAdamScalars {
+    float beta1;        /* _betta1                                  */
+    float beta2;        /* _betta2                                  */
+    float omb1;         /* 1 - _betta1                              */
+    float omb2;         /* 1 - _betta2                              */
+    float bc2;          /* _bias_correction2 = 1 / sqrt(1 - beta2^t) */
+    float eps;          /* _eps                                     */
+    float step_size;    /* -1 * _alpha / _bias_correction1          */
+    float w_decay;      /* -1 * _alpha * _weight_decay (AdamW)      */
+    float weight_decay; /* _weight_decay (L2 mode adds wd*p to g)   */
+    int32_t adamw_mode; /* 1 = decoupled decay, 0 = L2              */
+} SfAdamScalars;
+
+/* ---- optimizer objects: the scalar state machine --------------------------------------- */
+
+/* Replaces create_adam_optimizer (cpu_adam_impl.cpp:91-129).  Creates or overwrites the
+ * scalar block `id` (beta^t running products start at 1, step at 0). */
+int sf_adam_create(int id, float lr, float beta1, float beta2, float eps, float weight_decay,
+                   int adamw_mode, int should_log);
+
+/* Replaces destroy_adam_optimizer (cpu_adam_impl.cpp:272-277).  Unknown ids are ignored. */
+int sf_adam_destroy(int id);
+
+/* Advances optimizer `id` exactly like the first half of ds_adam_step
+ * (cpu_adam_impl.cpp:239-242: IncrementStep then update_state, cpu_adam.h:57-89) and
+ * writes the constants one element loop uses.  Host only; needs no GPU.  One call of this
+ * function corresponds to ONE reference adam_update call: the reference advances its state
+ * machine on every call, and whether beta^t comes from the running float product or from
+ * pow() depends on the call history. */
+int sf_adam_scalars(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, int bias_correction, SfAdamScalars* out);
+
+/* ---- the fused step, HBM-resident ------------------------------------------------------ */
+
+/* Replaces ds_adam_step / adam_update (cpu_adam_impl.cpp:220-270) for device buffers:
+ * sf_adam_scalars(id, ...) followed by sf_adam_step(...) with vec_n = n rounded down to 16.
+ *   p, m, v   fp32[n], updated in place
+ *   g         bf16[n] or fp32[n] according to g_dtype, read only
+ *   p_bf16    optional bf16[n] output: round-to-nearest-even copy of the UPDATED p, NaN ->
+ *             0x7FC0.  Replaces the reference's separate CPU cast, transformer_layer.py:296-305.
+ * Any n >= 0 and any natural element alignment is accepted.  The 128-bit vector kernel runs
+ * when p, m, v, g and p_bf16 are all 16-byte aligned, otherwise a scalar kernel runs. */
+int sf_adam_update(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
+                   float weight_decay, int bias_correction, float* p, const void* g,
+                   int g_dtype, float* m, float* v, uint16_t* p_bf16, uint64_t n, void* stream);
+
+/* The element loop alone, with explicit constants (Step_AVX, cpu_adam.h:108-197, plus the
+ * Step_1 tail, cpu_adam_impl.cpp:41-68).  Elements [0, vec_n) use the vector body's
+ * operation order, elements [vec_n, n) the tail's; a caller that updates a slice of what
+ * the reference would process in one call passes the slice-relative position of that call's
+ * (n_ref rounded down to 16) boundary, clamped to [0, n]. */
+int sf_adam_step(const SfAdamScalars* s, float* p, const void* g, int g_dtype, float* m,
+                 float* v, uint16_t* p_bf16, uint64_t n, uint64_t vec_n, void* stream);
+
+/* ---- the fused step with the data-parallel gradient mean folded in ---------------------- */
+
+/* Replaces SharedDataParallel.reduce_chunk's rank-0 arithmetic
+ * (multi_gpu/shared_data_parallel.py:130-136) for the slice this rank owns: for each element
+ * the kernel loads the `world` per-rank gradients through peer-mapped pointers, adds them to
+ * a zero fp32 accumulator in rank order 0..world-1, divides by world, and applies the step.
+ *   peer_g[r]  device pointer (local or peer-mapped) to rank r's gradient for THIS slice, n
+ *              elements of g_dtype; 1 <= world <= 16
+ * The caller must order this launch after every rank has finished writing its gradient and
+ * must keep the gradients unchanged until the launch completes (the kernel itself never
+ * waits on another GPU).  All pointers must be 16-byte aligned and n a multiple of 8, except
+ * that a scalar kernel handles any other case. */
+int sf_adam_step_sharded(const SfAdamScalars* s, float* p, const void* const* peer_g, int world,
+                         int g_dtype, float* m, float* v, uint16_t* p_bf16, uint64_t n,
+                         uint64_t vec_n, void* stream);
+
+/* ---- the fused step for host-resident state -------------------------------------------- */
+
+/* For optimizer state that does not fit in HBM: p, m, v live in PINNED host memory (the
+ * reference keeps them in pageable/pinned CPU tensors, transformer_layer.py:192-196 and
+ * layer_adam.py:163-173).  The call cuts [0, n) into chunks of chunk_elems, and for each
+ * chunk copies p, m, v host->device into one of two scratch slots, runs the kernel, and
+ * copies p, m, v device->host, with the three phases of neighbouring chunks overlapped on
+ * three internal side streams ordered by CUDA events.
+ *   g            gradient; g_on_host != 0 means pinned host memory (copied per chunk),
+ *                otherwise a device pointer
+ *   p_bf16_dev   optional DEVICE bf16[n] output (the window buffer the next forward reads)
+ *   scratch      device memory of at least sf_adam_host_scratch_bytes(chunk_elems, g_dtype,
+ *                g_on_host) bytes, 256-byte aligned, owned by the caller
+ *   stream       the work is ordered after everything already on `stream`, and `stream`
+ *                waits for the last device->host copy before later work runs
+ * chunk_elems must be a multiple of 16 (so every chunk but the last stays on the vector
+ * body, like the reference's 32 Mi-element chunks, transformer_layer.py:26-27).  The scalar
+ * state machine advances once (one reference call per chunk would take the pow() branch
+ * from the second chunk on; pass per_chunk_scalars != 0 to reproduce that). */
+size_t sf_adam_host_scratch_bytes(uint64_t chunk_elems, int g_dtype, int g_on_host);
+int sf_adam_update_host(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
+                        float weight_decay, int bias_correction, float* p_host,
+                        const void* g, int g_dtype, int g_on_host, float* m_host, float* v_host,
+                        uint16_t* p_bf16_dev, uint64_t n, uint64_t chunk_elems,
+                        int per_chunk_scalars, void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- plumbing -------------------------------------------------------------------------- */
+
+/* Message of the calling thread's most recent failing call ("" if none). */
+const char* sf_last_error(void);
+
+/* SF_ABI_VERSION the library was built with. */
+int sf_abi_version(void);
+
+/* Number of kernels this library has launched in the calling process (all threads). */
+uint64_t sf_launch_count(void);
+
+/* Access pattern and grid size of the vector kernel.  variant: 0 = 128-bit accesses with
+ * default caching, 1 = 128-bit accesses with streaming (evict-first) hints, 2 = 256-bit
+ * accesses.  ctas_per_sm: the persistent grid is SM count * ctas_per_sm CTAs of 256 threads.
+ * A negative variant or a ctas_per_sm <= 0 keeps the current setting.  Intended for
+ * benchmarking; the defaults are the measured best.  Not thread safe. */
+int sf_set_tuning(int variant, int ctas_per_sm);
+
+/* cudaIpc plumbing for the sharded path: export a handle for a cudaMalloc'ed base pointer
+ * and map a peer's handle into this process.  handle is SF_IPC_HANDLE_BYTES bytes. */
+#define SF_IPC_HANDLE_BYTES 64
+int sf_ipc_export(void* dev_ptr, void* handle_out);
+int sf_ipc_open(const void* handle, void** dev_ptr_out);
+int sf_ipc_close(void* dev_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLIDEFORMER_B200_H */

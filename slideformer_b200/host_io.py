@@ -1,0 +1,72 @@
+"""Chunked host <-> device plumbing around the fused step when the gradient arrives in host
+memory and the bf16 weights are wanted back in host memory.
+
+This is the boundary the reference crosses on every layer: its gradient chunks travel
+device -> host before the CPU Adam (transformer_layer.py:384-389) and the bf16 weights travel
+host -> device afterwards (transformer_layer.py:296-305).  With the optimizer state resident
+in HBM the directions flip: bf16 gradient in, bf16 weights out, 2 bytes per parameter each
+way, and the three phases of neighbouring chunks overlap on three CUDA streams.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .layer_adam import LayerAdam
+
+
+class HostGradStepper:
+    """Runs `LayerAdam.step_chunk` over a flat HBM-resident layer whose gradient is in pinned
+    host memory, optionally returning the bf16 copy of the updated weights to pinned host
+    memory.  Chunk k+1's upload, chunk k's kernel and chunk k-1's download run concurrently."""
+
+    def __init__(self, opt: LayerAdam, numel: int, device, chunk_numel: int = 32 * 1024 * 1024,
+                 grad_dtype=torch.bfloat16):
+        if chunk_numel % 16:
+            raise ValueError("chunk_numel must be a multiple of 16 so every chunk but the last stays on the vector body")
+        self.opt = opt
+        self.numel = int(numel)
+        self.device = torch.device(device)
+        self.chunk = int(chunk_numel)
+        with torch.cuda.device(self.device):
+            self.s_in = torch.cuda.Stream()
+            self.s_k = torch.cuda.Stream()
+            self.s_out = torch.cuda.Stream()
+            self.g_dev = [torch.empty(min(self.chunk, max(self.numel, 1)), dtype=grad_dtype, device=self.device)
+                          for _ in range(2)]
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]
+        self.ev_k = [torch.cuda.Event() for _ in range(2)]
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]
+
+    @torch.no_grad()
+    def step(self, p: torch.Tensor, g_host: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
+             bf16_dev: Optional[torch.Tensor], bf16_host: Optional[torch.Tensor], param_group: dict):
+        """One optimizer step.  p, m, v, bf16_dev: flat CUDA tensors; g_host, bf16_host: flat pinned
+        host tensors.  Returns after enqueueing; the caller's current stream waits for the end."""
+        n = self.numel
+        if not g_host.is_pinned() or (bf16_host is not None and not bf16_host.is_pinned()):
+            raise RuntimeError("host buffers must be pinned")
+        cur = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_k, self.s_out):
+            s.wait_stream(cur)
+        nchunks = (n + self.chunk - 1) // self.chunk
+        for k in range(nchunks):
+            slot = k & 1
+            a, b = k * self.chunk, min((k + 1) * self.chunk, n)
+            with torch.cuda.stream(self.s_in):
+                if k >= 2:
+                    self.s_in.wait_event(self.ev_k[slot])  # the kernel of chunk k-2 has consumed this slot
+                self.g_dev[slot][: b - a].copy_(g_host[a:b], non_blocking=True)
+                self.ev_in[slot].record(self.s_in)
+            with torch.cuda.stream(self.s_k):
+                self.s_k.wait_event(self.ev_in[slot])
+                self.opt.step_chunk(p[a:b], self.g_dev[slot][: b - a], m[a:b], v[a:b], param_group,
+                                    bf16_dev[a:b] if bf16_dev is not None else None)
+                self.ev_k[slot].record(self.s_k)
+            if bf16_host is not None and bf16_dev is not None:
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(self.ev_k[slot])
+                    bf16_host[a:b].copy_(bf16_dev[a:b], non_blocking=True)
+        cur.wait_stream(self.s_k)
+        cur.wait_stream(self.s_out)

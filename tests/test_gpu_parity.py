@@ -1,0 +1,460 @@
+"""Parity of the CUDA path with the CPU oracle and the reference's golden vectors.
+
+Every compute call goes through the C ABI (directly, or through LayerAdam which does nothing
+but marshal pointers).  Tolerance: 0 ulp.  north_star allows 2 ulp on p / m / v and asks for a
+bit-exact bf16 copy wherever the fp32 results agree; these tests assert bit equality of all
+four outputs, and NaN-ness where the result is a NaN (payloads are not compared).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from golden_cases import REFT, REFTEST_CHUNK, REFTEST_SIZES, TRAJ_CASES, reftest_lr
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from slideformer_b200 import _lib
+    L = _lib.load()
+    assert torch.cuda.is_available()
+    return L
+
+
+def to_dev_bf16(bits_u16: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits_u16.astype(np.uint16).view(np.int16).copy()).to(DEV).view(torch.bfloat16)
+
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def f32_bits(t: torch.Tensor) -> np.ndarray:
+    return t.detach().cpu().numpy().view(np.uint32)
+
+
+def assert_bits(got: torch.Tensor, want: np.ndarray, what=""):
+    g = f32_bits(got) if got.dtype == torch.float32 else bf16_bits(got)
+    w = want.view(np.uint32) if want.dtype == np.float32 else want
+    if not np.array_equal(g, w):
+        bad = np.nonzero(g != w)[0]
+        raise AssertionError(f"{what}: {bad.size} of {g.size} elements differ, first at {bad[0]}: "
+                             f"got {g[bad[0]]:#x} want {w[bad[0]]:#x}")
+
+
+# ------------------------------------------------------------------------------------------
+# golden vectors from the compiled reference
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("name", sorted(TRAJ_CASES))
+def test_golden_trajectories(name, variant, golden, lib):
+    from slideformer_b200 import LayerAdam
+    lib.sf_set_tuning(variant, 0)
+    try:
+        hp, adamw, bc, steps = TRAJ_CASES[name]
+        p = torch.from_numpy(golden[f"{name}/p0"].copy()).to(DEV)
+        n = p.numel()
+        m = torch.zeros(n, device=DEV)
+        v = torch.zeros(n, device=DEV)
+        out = torch.zeros(n, device=DEV, dtype=torch.bfloat16)
+        g_all = golden[f"{name}/g"]
+        bounds = golden[f"{name}/bounds"]
+        opt = LayerAdam(lr=hp["lr"], betas=(hp["b1"], hp["b2"]), eps=hp["eps"], weight_decay=hp["wd"],
+                        adamw_mode=adamw, bias_correction=bc)
+        for step in range(1, steps + 1):
+            gnp = g_all[step - 1]
+            g = to_dev_bf16(gnp) if gnp.dtype == np.uint16 else torch.from_numpy(gnp.copy()).to(DEV)
+            group = dict(opt.defaults, step=step)
+            for a, b in zip(bounds[:-1], bounds[1:]):
+                if b > a:
+                    opt.step_chunk(p[a:b], g[a:b], m[a:b], v[a:b], group, out[a:b])
+            tag = f"{name}/s{step}"
+            if f"{tag}/p" in golden:
+                assert_bits(p, golden[f"{tag}/p"], f"{tag} p")
+                assert_bits(m, golden[f"{tag}/m"], f"{tag} m")
+                assert_bits(v, golden[f"{tag}/v"], f"{tag} v")
+                assert_bits(out, golden[f"{tag}/bf16"], f"{tag} bf16")
+    finally:
+        lib.sf_set_tuning(1, 0)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("fused", [False, True])
+def test_reference_dp_test_sequence(dt, fused, golden, lib):
+    """The reference's own test sequence (19 / 3 / 0 elements, chunks of 5, two ranks, lr change).
+    fused=False: mean on the device with torch in rank order, then step_chunk (the
+    <float, float, float> triple).  fused=True: sf_adam_step_sharded reads both ranks' rows."""
+    from slideformer_b200 import LayerAdam, _lib
+    opt = LayerAdam(lr=0.01, betas=(REFT["b1"], REFT["b2"]), eps=REFT["eps"], weight_decay=REFT["wd"])
+    ps = [torch.from_numpy(golden[f"reftest/{dt}/L{i}/p0"].copy()).to(DEV) for i in range(3)]
+    ms = [torch.zeros_like(p) for p in ps]
+    vs = [torch.zeros_like(p) for p in ps]
+    for step in range(1, 6):
+        lr = reftest_lr(step)
+        for li, size in enumerate(REFTEST_SIZES):
+            rows_np = golden[f"reftest/{dt}/L{li}/g{step}"]
+            rows = to_dev_bf16(rows_np.reshape(-1)).view(2, size) if dt == "bf16" else torch.from_numpy(rows_np.copy()).to(DEV)
+            for s in range(0, size, REFTEST_CHUNK):
+                e = min(s + REFTEST_CHUNK, size)
+                if not fused:
+                    mean = torch.zeros(e - s, device=DEV)
+                    for peer in range(2):
+                        mean.add_(rows[peer, s:e])
+                    mean.div_(2)
+                    opt.step_chunk(ps[li][s:e], mean, ms[li][s:e], vs[li][s:e], dict(opt.defaults, step=step, lr=lr))
+                else:
+                    sc = _lib.SfAdamScalars()
+                    _lib.check(lib.sf_adam_scalars(opt.optimizer_id, step, lr, REFT["b1"], REFT["b2"], REFT["eps"],
+                                                   REFT["wd"], 1, C.byref(sc)))
+                    peers = (C.c_void_p * 2)(rows[0, s:e].data_ptr(), rows[1, s:e].data_ptr())
+                    n = e - s
+                    _lib.check(lib.sf_adam_step_sharded(
+                        C.byref(sc), ps[li][s:e].data_ptr(), peers, 2,
+                        _lib.SF_GRAD_BF16 if dt == "bf16" else _lib.SF_GRAD_F32,
+                        ms[li][s:e].data_ptr(), vs[li][s:e].data_ptr(), None, n, n & ~15,
+                        torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    for li in range(3):
+        assert_bits(ps[li], golden[f"reftest/{dt}/L{li}/p"], f"L{li} p")
+        assert_bits(ms[li], golden[f"reftest/{dt}/L{li}/m"], f"L{li} m")
+        assert_bits(vs[li], golden[f"reftest/{dt}/L{li}/v"], f"L{li} v")
+
+
+# ------------------------------------------------------------------------------------------
+# seeded random inputs against the oracle
+# ------------------------------------------------------------------------------------------
+def run_both(oracle, lib, n, steps, hp, adamw=True, bc=True, gdtype=torch.bfloat16, with_out=True, seed=0,
+             special=False):
+    from slideformer_b200 import LayerAdam
+    gen = torch.Generator().manual_seed(seed)
+    p0 = torch.randn(n, generator=gen) * 0.02
+    if special and n >= 64:
+        p0[:8] = torch.tensor([0.0, -0.0, float("inf"), -float("inf"), 1e-42, -1e-45, 3e38, 1.0])
+    po, mo, vo = p0.numpy().copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    oo = np.zeros(n, np.uint16) if with_out else None
+    pd, md, vd = p0.to(DEV), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    od = torch.zeros(n, device=DEV, dtype=torch.bfloat16) if with_out else None
+    orc = oracle.OracleAdam(hp[0], hp[1], hp[2], hp[3], hp[4], adamw)
+    opt = LayerAdam(lr=hp[0], betas=(hp[1], hp[2]), eps=hp[3], weight_decay=hp[4], adamw_mode=adamw,
+                    bias_correction=bc)
+    for step in range(1, steps + 1):
+        g = torch.randn(n, generator=gen) * 1e-3
+        if special and n >= 64:
+            g[8:16] = torch.tensor([0.0, -0.0, 1e-30, -1e-22, float("inf"), 65504.0, 1e-40, -1e-38])
+            g[16:24] = 0.0
+        g = g.to(gdtype)
+        gnp = g.view(torch.int16).numpy().view(np.uint16) if gdtype == torch.bfloat16 else g.numpy()
+        orc.adam_update(step, hp[0], hp[1], hp[2], hp[3], hp[4], bc, po, gnp, mo, vo, oo)
+        opt.step_chunk(pd, g.to(DEV), md, vd, dict(opt.defaults, step=step), od)
+    torch.cuda.synchronize()
+    return (po, mo, vo, oo), (pd, md, vd, od)
+
+
+def compare(cpu, gpu, allow_nan=False):
+    for name, a, b in zip("pmvo", cpu, gpu):
+        if a is None:
+            continue
+        if a.dtype == np.float32:
+            gb = b.cpu().numpy()
+            if allow_nan:
+                both_nan = np.isnan(a) & np.isnan(gb)
+                assert np.array_equal(a.view(np.uint32)[~both_nan], gb.view(np.uint32)[~both_nan]), name
+            else:
+                assert_bits(b, a, name)
+        else:
+            gb = bf16_bits(b)
+            if allow_nan:
+                nan_c = (a & 0x7FFF) > 0x7F80
+                assert np.array_equal(nan_c, (gb & 0x7FFF) > 0x7F80)
+                assert np.all(gb[nan_c] == 0x7FC0), "NaN must be stored as 0x7FC0"
+                assert np.array_equal(a[~nan_c], gb[~nan_c]), name
+            else:
+                assert_bits(b, a, name)
+
+
+CFG0 = (1e-5, 0.9, 0.999, 1e-8, 0.01)
+REFHP = (0.01, 0.8, 0.95, 1e-6, 0.1)
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("n", [4, 7, 8, 31, 2047, 2048, 2049, 4096 + 16, (1 << 20) + 13, 3 * (1 << 20)])
+def test_sizes_vs_oracle(n, variant, oracle, lib):
+    lib.sf_set_tuning(variant, 0)
+    try:
+        compare(*run_both(oracle, lib, n, 3, CFG0, seed=n))
+    finally:
+        lib.sf_set_tuning(1, 0)
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("adamw,bc,wd,gdtype,with_out", [
+    (True, True, 0.01, torch.bfloat16, True),
+    (True, True, 0.01, torch.float32, True),
+    (False, True, 0.1, torch.bfloat16, True),
+    (False, True, 0.1, torch.float32, False),
+    (True, False, 0.01, torch.bfloat16, False),
+    (True, True, 0.0, torch.bfloat16, True),
+    (False, False, 0.0, torch.float32, True),
+])
+def test_modes_vs_oracle(adamw, bc, wd, gdtype, with_out, variant, oracle, lib):
+    lib.sf_set_tuning(variant, 0)
+    try:
+        hp = (REFHP[0], REFHP[1], REFHP[2], REFHP[3], wd)
+        compare(*run_both(oracle, lib, 70001, 4, hp, adamw, bc, gdtype, with_out, seed=11))
+    finally:
+        lib.sf_set_tuning(1, 0)
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_special_values(variant, oracle, lib):
+    """Zeros, signed zero, infinities, subnormals, huge values; NaN results compare as NaN."""
+    lib.sf_set_tuning(variant, 0)
+    try:
+        compare(*run_both(oracle, lib, 4096, 3, CFG0, special=True, seed=5), allow_nan=True)
+    finally:
+        lib.sf_set_tuning(1, 0)
+
+
+def test_misaligned_slices_take_the_scalar_kernel(oracle, lib):
+    """Slices starting at odd element offsets (the reference accepts any slice)."""
+    from slideformer_b200 import LayerAdam
+    n = 5000
+    gen = torch.Generator().manual_seed(3)
+    p0 = torch.randn(n + 3, generator=gen) * 0.02
+    g0 = (torch.randn(n + 3, generator=gen) * 1e-3).to(torch.bfloat16)
+    for off in (1, 2, 3):
+        po = p0.numpy().copy()[off:off + n]
+        mo, vo, oo = np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.uint16)
+        orc = oracle.OracleAdam(*CFG0, True)
+        orc.adam_update(1, *CFG0, True, po, g0.view(torch.int16).numpy().view(np.uint16)[off:off + n].copy(), mo, vo, oo)
+        pd = p0.to(DEV)
+        md, vd = torch.zeros(n + 3, device=DEV), torch.zeros(n + 3, device=DEV)
+        od = torch.zeros(n + 3, device=DEV, dtype=torch.bfloat16)
+        opt = LayerAdam(lr=CFG0[0], betas=CFG0[1:3], eps=CFG0[3], weight_decay=CFG0[4])
+        opt.step_chunk(pd[off:off + n], g0.to(DEV)[off:off + n], md[off:off + n], vd[off:off + n],
+                       dict(opt.defaults, step=1), od[off:off + n])
+        compare((po, mo, vo, oo), (pd[off:off + n], md[off:off + n], vd[off:off + n], od[off:off + n]))
+        # nothing outside the slice was touched
+        assert torch.equal(pd[:off].cpu(), p0[:off]) and torch.equal(pd[off + n:].cpu(), p0[off + n:])
+        assert not md[:off].any() and not md[off + n:].any()
+
+
+def test_explicit_vec_n_slices_reproduce_one_reference_call(oracle, lib):
+    """A reference call over n elements, executed as three slices with slice-relative vec_n."""
+    from slideformer_b200 import _lib
+    n = 16 * 700 + 11
+    gen = torch.Generator().manual_seed(21)
+    p0 = torch.randn(n, generator=gen) * 0.02
+    g = (torch.randn(n, generator=gen) * 1e-3).to(torch.bfloat16)
+    po, mo, vo = p0.numpy().copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    orc = oracle.OracleAdam(*CFG0, True)
+    orc.adam_update(1, *CFG0, True, po, g.view(torch.int16).numpy().view(np.uint16), mo, vo)
+    sid = 31337
+    _lib.check(lib.sf_adam_create(sid, *CFG0, 1, 0))
+    sc = _lib.SfAdamScalars()
+    _lib.check(lib.sf_adam_scalars(sid, 1, *CFG0, 1, C.byref(sc)))
+    pd, gd = p0.to(DEV), g.to(DEV)
+    md, vd = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    vec_ref = n & ~15
+    cuts = [0, 16 * 300, 16 * 650, n]
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        vec_local = min(max(vec_ref - a, 0), b - a)
+        _lib.check(lib.sf_adam_step(C.byref(sc), pd[a:b].data_ptr(), gd[a:b].data_ptr(), _lib.SF_GRAD_BF16,
+                                    md[a:b].data_ptr(), vd[a:b].data_ptr(), None, b - a, vec_local,
+                                    torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    compare((po, mo, vo, None), (pd, md, vd, None))
+    lib.sf_adam_destroy(sid)
+
+
+# ------------------------------------------------------------------------------------------
+# LayerAdam whole-layer API
+# ------------------------------------------------------------------------------------------
+def test_layer_step_api_matches_reference_call_sequence(oracle, lib):
+    """Two layers, several parameters each, step() and step_with_grad_views(): one reference
+    adam_update per parameter on one shared optimizer object (layer_adam.py:297-340)."""
+    from slideformer_b200 import LayerAdam
+    hp = (3e-4, 0.9, 0.999, 1e-8, 0.01)
+    shapes = [[(64, 48), (48,), (33, 7)], [(128, 16), (5,)]]
+    gen = torch.Generator().manual_seed(99)
+    opt = LayerAdam(lr=hp[0], betas=hp[1:3], eps=hp[3], weight_decay=hp[4], num_layer=2)
+    orc = oracle.OracleAdam(*hp, True)
+    layers, cpu = [], []
+    for li, shp in enumerate(shapes):
+        numel = sum(int(np.prod(s)) for s in shp)
+        flat = (torch.randn(numel, generator=gen) * 0.02)
+        flat_d = flat.to(DEV)
+        bf = torch.zeros(numel, device=DEV, dtype=torch.bfloat16)
+        params, bfs, off = [], [], 0
+        for s in shp:
+            k = int(np.prod(s))
+            params.append(torch.nn.Parameter(flat_d[off:off + k].view(s), requires_grad=False))
+            bfs.append(bf[off:off + k].view(s))
+            off += k
+        assert opt.add_layer_params(li, params, bfs) == li
+        layers.append((params, flat_d, bf))
+        cpu.append((flat.numpy().copy(), np.zeros(numel, np.float32), np.zeros(numel, np.float32), np.zeros(numel, np.uint16)))
+    assert opt.exp_avg_flat[0].device.type == "cuda" and opt.exp_avg_flat[0].numel() == layers[0][1].numel()
+    for it in range(3):
+        for li in (1, 0):  # backward order
+            params, flat_d, bf = layers[li]
+            numel = flat_d.numel()
+            # p.grad must have the parameter's dtype, so step() runs the <float, float, float>
+            # triple and step_with_grad_views() the <float, bf16, float> one
+            g = torch.randn(numel, generator=gen) * 1e-3
+            if it % 2 == 1:
+                g = g.to(torch.bfloat16)
+            gd = g.to(DEV)
+            off, views = 0, {}
+            for p in params:
+                views[p] = gd[off:off + p.numel()].view(p.shape)
+                off += p.numel()
+            if it % 2 == 0:
+                for p in params:
+                    p.grad = views[p]
+                opt.step(li)
+            else:
+                opt.step_with_grad_views(li, views)
+            po, mo, vo, oo = cpu[li]
+            gnp = g.view(torch.int16).numpy().view(np.uint16) if g.dtype == torch.bfloat16 else g.numpy()
+            off = 0
+            for p in params:
+                k = p.numel()
+                orc.adam_update(it + 1, *hp, True, po[off:off + k], gnp[off:off + k], mo[off:off + k],
+                                vo[off:off + k], oo[off:off + k])
+                off += k
+            assert opt.param_groups[li]["step"] == it + 1
+    torch.cuda.synchronize()
+    for li in range(2):
+        params, flat_d, bf = layers[li]
+        compare(cpu[li], (flat_d, opt.exp_avg_flat[li], opt.exp_avg_sq_flat[li], bf))
+        st = opt.state[params[0]]
+        assert st["exp_avg"].shape == params[0].shape and st["exp_avg"].data_ptr() == opt.exp_avg_flat[li].data_ptr()
+
+
+def test_error_behaviour(lib):
+    from slideformer_b200 import LayerAdam
+    opt = LayerAdam(lr=1e-3)
+    z = torch.zeros(64, device=DEV)
+    grp = dict(opt.defaults, step=1)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        opt.step_chunk(z[::2], z[:32].clone(), z[:32].clone(), z[:32].clone(), grp)
+    with pytest.raises(RuntimeError, match="not supported"):
+        opt.step_chunk(z, z.to(torch.float16), z.clone(), z.clone(), grp)
+    with pytest.raises(RuntimeError, match="same number"):
+        opt.step_chunk(z, z[:32].clone(), z.clone(), z.clone(), grp)
+    with pytest.raises(RuntimeError, match="same CUDA device"):
+        opt.step_chunk(z, torch.zeros(64), z.clone(), z.clone(), grp)
+    # empty chunk is fine (the reference test has a 0-element layer)
+    e = torch.zeros(0, device=DEV)
+    opt.step_chunk(e, e.clone(), e.clone(), e.clone(), grp)
+    before = lib.sf_launch_count()
+    opt.step_chunk(z, z.clone().to(torch.bfloat16), z.clone(), z.clone(), grp)
+    assert lib.sf_launch_count() == before + 1
+
+
+# ------------------------------------------------------------------------------------------
+# host-resident state streamed through the GPU
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("g_on_host", [False, True])
+@pytest.mark.parametrize("n,chunk", [(4096 * 5 + 37, 4096), (100000, 1 << 20), (16, 16), (3 * 65536, 65536)])
+def test_host_streaming_path(n, chunk, g_on_host, oracle, lib):
+    from slideformer_b200 import LayerAdam
+    gen = torch.Generator().manual_seed(n)
+    p0 = torch.randn(n, generator=gen) * 0.02
+    po, mo, vo, oo = p0.numpy().copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.uint16)
+    ph = p0.clone().pin_memory()
+    mh, vh = torch.zeros(n).pin_memory(), torch.zeros(n).pin_memory()
+    od = torch.zeros(n, device=DEV, dtype=torch.bfloat16)
+    opt = LayerAdam(lr=CFG0[0], betas=CFG0[1:3], eps=CFG0[3], weight_decay=CFG0[4], stream_chunk_numel=chunk)
+    orc = oracle.OracleAdam(*CFG0, True)
+    nchunks = (n + chunk - 1) // chunk
+    for step in range(1, 4):
+        g = (torch.randn(n, generator=gen) * 1e-3).to(torch.bfloat16)
+        gnp = g.view(torch.int16).numpy().view(np.uint16)
+        # the streamed step is one reference call per chunk boundary-wise (each chunk ends its own
+        # 16-lane body) but advances the scalar state once
+        c = orc.scalars(step, *CFG0, True)
+        for k in range(nchunks):
+            a, b = k * chunk, min((k + 1) * chunk, n)
+            oracle.apply_step(c, po[a:b], gnp[a:b], mo[a:b], vo[a:b], oo[a:b])
+        gg = g.pin_memory() if g_on_host else g.to(DEV)
+        opt.step_chunk(ph, gg, mh, vh, dict(opt.defaults, step=step), od)
+        torch.cuda.synchronize()
+    compare((po, mo, vo, oo), (ph, mh, vh, od))
+
+
+# ------------------------------------------------------------------------------------------
+# full benchmark size: properties that do not need a CPU pass over everything, plus one that does
+# ------------------------------------------------------------------------------------------
+N_LAYER = 218_112_000  # one Llama-3.1-8B decoder layer, flattened
+
+
+def test_full_layer_properties(oracle, lib):
+    from slideformer_b200 import LayerAdam
+    n = N_LAYER
+    gen = torch.Generator(device=DEV).manual_seed(1234)
+    p0 = torch.randn(n, device=DEV, generator=gen) * 0.02
+    p0[-8192:] = 1.0
+    g = (torch.randn(n, device=DEV, generator=gen) * 1e-3).to(torch.bfloat16)
+    results = []
+    for variant in (0, 1, 2):
+        lib.sf_set_tuning(variant, 0)
+        p, m, v = p0.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+        out = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+        opt = LayerAdam(lr=CFG0[0], betas=CFG0[1:3], eps=CFG0[3], weight_decay=CFG0[4])
+        for step in (1, 2):
+            opt.step_chunk(p, g, m, v, dict(opt.defaults, step=step), out)
+        torch.cuda.synchronize()
+        results.append((p, m, v, out))
+    lib.sf_set_tuning(1, 0)
+    # (1) the three access patterns agree on every bit of every output
+    for other in results[1:]:
+        for a, b in zip(results[0], other):
+            assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a.view(torch.int16),
+                               b.view(torch.int32) if b.dtype == torch.float32 else b.view(torch.int16))
+    p, m, v, out = results[0]
+    # (2) the fused bf16 output is the RNE cast of the fp32 result over the whole layer
+    assert torch.equal(out.view(torch.int16), p.to(torch.bfloat16).view(torch.int16))
+    # (3) windows at the start, across an interior tile boundary and at the end match the oracle
+    for lo, hi in ((0, 1 << 20), (n // 2 - 70001, n // 2 + 70001), (n - (1 << 20) - 5, n)):
+        po = p0[lo:hi].cpu().numpy().copy()
+        k = hi - lo
+        mo, vo, oo = np.zeros(k, np.float32), np.zeros(k, np.float32), np.zeros(k, np.uint16)
+        gnp = bf16_bits(g[lo:hi])
+        orc = oracle.OracleAdam(*CFG0, True)
+        for step in (1, 2):
+            orc.adam_update(step, *CFG0, True, po, gnp, mo, vo, oo, vec_n=k)  # n is a multiple of 16: all body
+        compare((po, mo, vo, oo), (p[lo:hi], m[lo:hi], v[lo:hi], out[lo:hi]))
+
+
+def test_full_layer_trajectory_vs_oracle(oracle, lib):
+    """Config 0 at full size: every element of p, m, v and the bf16 copy after 2 steps."""
+    from slideformer_b200 import LayerAdam
+    n = N_LAYER
+    torch.set_num_threads(max(1, torch.get_num_threads()))
+    gen = torch.Generator().manual_seed(0)
+    p0 = torch.empty(n).normal_(0, 0.02, generator=gen)
+    p0[-8192:] = 1.0
+    po, mo, vo, oo = p0.numpy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.uint16)
+    pd, md, vd = p0.to(DEV), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    od = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    po = po.copy()
+    opt = LayerAdam(lr=CFG0[0], betas=CFG0[1:3], eps=CFG0[3], weight_decay=CFG0[4])
+    orc = oracle.OracleAdam(*CFG0, True)
+    for step in (1, 2):
+        g = torch.empty(n).normal_(0, 1e-3, generator=gen).to(torch.bfloat16)
+        orc.adam_update(step, *CFG0, True, po, g.view(torch.int16).numpy().view(np.uint16), mo, vo, oo)
+        opt.step_chunk(pd, g.to(DEV), md, vd, dict(opt.defaults, step=step), od)
+    torch.cuda.synchronize()
+    for name, a, b in (("p", po, pd), ("m", mo, md), ("v", vo, vd)):
+        ref = torch.from_numpy(a).to(DEV)
+        assert torch.equal(ref.view(torch.int32), b.view(torch.int32)), name
+        del ref
+    ref = torch.from_numpy(oo.view(np.int16)).to(DEV)
+    assert torch.equal(ref, od.view(torch.int16))
