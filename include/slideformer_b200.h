@@ -118,6 +118,11 @@ int sf_adam_step_sharded(const SfAdamScalars* s, float* p, const void* const* pe
                          int g_dtype, float* m, float* v, uint16_t* p_bf16, uint64_t n,
                          uint64_t vec_n, void* stream);
 
+/* The gradient mean alone, for callers that keep the reference's update(params, mean, m, v)
+ * callback (shared_data_parallel.py:130-135): mean[i] = (0 + g_0[i] + ... + g_{world-1}[i]) / world
+ * in fp32, rank order.  mean is a local fp32[n] device buffer. */
+int sf_dp_mean(const void* const* peer_g, int world, int g_dtype, float* mean, uint64_t n, void* stream);
+
 /* ---- the fused step for host-resident state -------------------------------------------- */
 
 /* For optimizer state that does not fit in HBM: p, m, v live in PINNED host memory (the
@@ -157,14 +162,19 @@ uint64_t sf_launch_count(void);
 
 /* Access pattern and grid size of the vector kernel.  variant: 0 = 128-bit accesses with
  * default caching, 1 = 128-bit accesses with streaming (evict-first) hints, 2 = 256-bit
- * accesses.  ctas_per_sm: the persistent grid is SM count * ctas_per_sm CTAs of 256 threads.
- * A negative variant or a ctas_per_sm <= 0 keeps the current setting.  Intended for
- * benchmarking; the defaults are the measured best.  Not thread safe. */
+ * accesses.  ctas_per_sm: 0 = one 2048-element tile per CTA; k > 0 = persistent grid of SM
+ * count * k CTAs of 256 threads walking the tiles.  A negative value keeps the current
+ * setting.  Intended for benchmarking; the defaults (1, 0) are the measured best.  Not thread
+ * safe. */
 int sf_set_tuning(int variant, int ctas_per_sm);
 
 /* cudaIpc plumbing for the sharded path: export a handle for a cudaMalloc'ed base pointer
  * and map a peer's handle into this process.  handle is SF_IPC_HANDLE_BYTES bytes. */
 #define SF_IPC_HANDLE_BYTES 64
+/* Plain cudaMalloc / cudaFree on the current device, for buffers that must be the base of an
+ * allocation so that an IPC handle can be exported for them. */
+int sf_dev_alloc(size_t bytes, void** dev_ptr_out);
+int sf_dev_free(void* dev_ptr);
 int sf_ipc_export(void* dev_ptr, void* handle_out);
 int sf_ipc_open(const void* handle, void** dev_ptr_out);
 int sf_ipc_close(void* dev_ptr);

@@ -45,6 +45,7 @@ SIGNATURES = {
     "sf_adam_step": (_i, [C.POINTER(SfAdamScalars), _vp, _vp, _i, _vp, _vp, _vp, _u64, _u64, _vp]),
     "sf_adam_step_sharded": (_i, [C.POINTER(SfAdamScalars), _vp, C.POINTER(_vp), _i, _i, _vp, _vp, _vp,
                                   _u64, _u64, _vp]),
+    "sf_dp_mean": (_i, [C.POINTER(_vp), _i, _i, _vp, _u64, _vp]),
     "sf_adam_host_scratch_bytes": (C.c_size_t, [_u64, _i, _i]),
     "sf_adam_update_host": (_i, [_i, _u64, _f, _f, _f, _f, _f, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _u64,
                                  _u64, _i, _vp, C.c_size_t, _vp]),
@@ -52,6 +53,8 @@ SIGNATURES = {
     "sf_abi_version": (_i, []),
     "sf_launch_count": (_u64, []),
     "sf_set_tuning": (_i, [_i, _i]),
+    "sf_dev_alloc": (_i, [C.c_size_t, C.POINTER(_vp)]),
+    "sf_dev_free": (_i, [_vp]),
     "sf_ipc_export": (_i, [_vp, _vp]),
     "sf_ipc_open": (_i, [_vp, C.POINTER(_vp)]),
     "sf_ipc_close": (_i, [_vp]),

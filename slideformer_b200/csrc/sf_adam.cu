@@ -439,12 +439,29 @@ adam_vec8_kernel(K c, float* __restrict__ p, const void* __restrict__ gptr, floa
     }
 }
 
+// fp32 rank-ordered mean of the peers' gradients, 4 elements per thread-iteration.
+template <typename GS>
+__global__ void __launch_bounds__(256)
+dp_mean_kernel(GS gs, float* __restrict__ mean, uint64_t nvec, uint64_t n)
+{
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 4;
+    for (uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < nvec; i += stride) {
+        float o[4];
+        gs.template load4<1>(i, o);
+        __stcs(reinterpret_cast<float4*>(mean + i), make_float4(o[0], o[1], o[2], o[3]));
+    }
+    if (blockIdx.x == gridDim.x - 1)
+        for (uint64_t i = nvec + threadIdx.x; i < n; i += blockDim.x) mean[i] = gs.load1(i);
+}
+
 // ------------------------------------------------------------------------------------------
 // launch plumbing
 // ------------------------------------------------------------------------------------------
 struct Tuning {
     int variant = 1;      // 0: 128-bit default caching, 1: 128-bit streaming hints, 2: 256-bit
-    int ctas_per_sm = 8;  // persistent grid = SMs * ctas_per_sm (capped by the tile count)
+    int ctas_per_sm = 0;  // 0: one tile per CTA (measured best: the hardware CTA scheduler keeps
+                          // loads and stores of different CTAs interleaved); k > 0: persistent
+                          // grid of SMs * k CTAs walking the tiles
 };
 Tuning g_tune;
 
@@ -495,7 +512,7 @@ int dispatch_mode_out(int mode, bool has_out, F&& f)
 
 int grid_for(uint64_t ntiles, int sms, int ctas_per_sm)
 {
-    uint64_t cap = (uint64_t)sms * (uint64_t)ctas_per_sm;
+    uint64_t cap = ctas_per_sm > 0 ? (uint64_t)sms * (uint64_t)ctas_per_sm : (uint64_t)0x7fffffff;
     uint64_t g = ntiles < cap ? ntiles : cap;
     return (int)(g < 1 ? 1 : g);
 }
@@ -746,6 +763,40 @@ int sf_adam_step_sharded(const SfAdamScalars* s, float* p, const void* const* pe
     return launch_vec4(c, mode, p, gs, m, v, p_bf16, n, vec_n, st, 1);
 }
 
+int sf_dp_mean(const void* const* peer_g, int world, int g_dtype, float* mean, uint64_t n, void* stream)
+{
+    if (g_dtype != SF_GRAD_BF16 && g_dtype != SF_GRAD_F32)
+        return fail(SF_ERR_DTYPE, "gradient dtype code " + std::to_string(g_dtype) + " is not supported (0 = bf16, 1 = fp32)");
+    if (world < 1 || world > SF_MAX_WORLD)
+        return fail(SF_ERR_ARG, "world must be in [1, " + std::to_string(SF_MAX_WORLD) + "]");
+    if (n == 0) return SF_OK;
+    if (!peer_g || !mean) return fail(SF_ERR_NULL, "peer_g and mean must be non-NULL when n > 0");
+    bool a16 = aligned(mean, 16);
+    for (int r = 0; r < world; r++) {
+        if (!peer_g[r]) return fail(SF_ERR_NULL, "peer_g[" + std::to_string(r) + "] is NULL");
+        a16 = a16 && aligned(peer_g[r], 16);
+    }
+    DevInfo di;
+    if (int rc = device_info(&di)) return rc;
+    const uint64_t nvec = a16 ? (n & ~(uint64_t)3) : 0;
+    int grid = grid_for((n + 1023) / 1024, di.sms, 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (g_dtype == SF_GRAD_BF16) {
+        GradPeers<uint16_t> gs;
+        for (int r = 0; r < SF_MAX_WORLD; r++) gs.g[r] = (const uint16_t*)peer_g[r < world ? r : 0];
+        gs.world = world;
+        gs.fworld = (float)world;
+        dp_mean_kernel<<<grid, 256, 0, st>>>(gs, mean, nvec, n);
+    } else {
+        GradPeers<float> gs;
+        for (int r = 0; r < SF_MAX_WORLD; r++) gs.g[r] = (const float*)peer_g[r < world ? r : 0];
+        gs.world = world;
+        gs.fworld = (float)world;
+        dp_mean_kernel<<<grid, 256, 0, st>>>(gs, mean, nvec, n);
+    }
+    return check_launch("dp_mean_kernel");
+}
+
 size_t sf_adam_host_scratch_bytes(uint64_t chunk_elems, int g_dtype, int g_on_host)
 {
     size_t per_slot = 3 * round256((size_t)chunk_elems * 4);
@@ -836,7 +887,23 @@ int sf_set_tuning(int variant, int ctas_per_sm)
 {
     if (variant > 2) return fail(SF_ERR_ARG, "variant must be 0 (128-bit, default caching), 1 (128-bit, streaming) or 2 (256-bit)");
     if (variant >= 0) g_tune.variant = variant;
-    if (ctas_per_sm > 0) g_tune.ctas_per_sm = ctas_per_sm;
+    if (ctas_per_sm >= 0) g_tune.ctas_per_sm = ctas_per_sm;
+    return SF_OK;
+}
+
+int sf_dev_alloc(size_t bytes, void** dev_ptr_out)
+{
+    if (!dev_ptr_out) return fail(SF_ERR_NULL, "dev_ptr_out is NULL");
+    *dev_ptr_out = nullptr;
+    if (bytes == 0) return SF_OK;
+    SF_CUDA(cudaMalloc(dev_ptr_out, bytes));
+    return SF_OK;
+}
+
+int sf_dev_free(void* dev_ptr)
+{
+    if (!dev_ptr) return SF_OK;
+    SF_CUDA(cudaFree(dev_ptr));
     return SF_OK;
 }
 

@@ -1,0 +1,414 @@
+"""Single-node data parallelism with the optimizer state sharded 1/N across the GPUs.
+
+Mirror of the reference's `SharedDataParallel` (multi_gpu/shared_data_parallel.py:21-148):
+same constructor keywords, `register_layer`, `reduce_chunk(layer, start, end, local_grad,
+update)`, `barrier`, `raise_if_failed`, `close`, and the attributes `rank`, `world_size`,
+`chunk_numel`, `dtype`, `layers`, `error`, `directory`.
+
+What changes.  The reference funnels every rank's gradient chunk through a /dev/shm slab,
+lets rank 0 average them in fp32 and run the CPU Adam, and shares one fp32 weight mapping.
+Here every rank owns a contiguous 1/N slice of each layer's fp32 weights and Adam moments in
+its own HBM.  Gradients stay on the GPUs in an exchange buffer that every rank maps from
+every other rank (CUDA IPC over NVLink); the owner of a slice reads the N per-rank gradients
+with plain loads, adds them to a zero fp32 accumulator in rank order and divides by N, which
+is the reference's arithmetic (shared_data_parallel.py:130-133) bit for bit, either into an
+fp32 buffer handed to the caller's `update` callback or directly inside the fused Adam
+kernel (`fused_update`).  The bf16 weights of all slices are then all-gathered with NCCL.
+
+Ordering between ranks uses stream-ordered NCCL operations only (a one-element all-reduce as
+a barrier, the all-gather itself); no kernel of this package ever waits on another GPU.
+A gloo group carries the host-side control plane: consistency checks and error flags.
+
+Exactness: results equal the reference's rank-0 update bit for bit when chunk starts are
+multiples of 16 elements (slice boundaries always are), because a chunk cut at a slice
+boundary then keeps the reference's 16-lane body / scalar tail split.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import socket
+from dataclasses import dataclass, field
+from datetime import timedelta
+from typing import Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+SHARD_ALIGN = 16  # elements; keeps every slice on the vector body and 32-byte aligned in fp32
+
+
+def shard_numel(numel: int, world: int, align: int = SHARD_ALIGN) -> int:
+    """Elements per rank: ceil(numel / world) rounded up to `align` (0 for an empty layer)."""
+    if numel <= 0:
+        return 0
+    per = -(-numel // world)
+    return -(-per // align) * align
+
+
+def shard_range(numel: int, world: int, rank: int, align: int = SHARD_ALIGN):
+    """Global [start, end) of the slice `rank` owns, clipped to the layer (may be empty)."""
+    s = shard_numel(numel, world, align)
+    a = min(rank * s, numel)
+    b = min((rank + 1) * s, numel)
+    return a, b
+
+
+@dataclass
+class LayerState:
+    """Per-layer state.  `params`, `exp_avg`, `exp_avg_sq` keep the reference's names but hold
+    THIS RANK's slice (every rank has one; the reference gives the moments to rank 0 only)."""
+    params: torch.Tensor
+    exp_avg: Optional[torch.Tensor]
+    exp_avg_sq: Optional[torch.Tensor]
+    step: int = 0
+    numel: int = 0
+    shard: int = 0           # slice length including padding (same on every rank)
+    start: int = 0           # global range of the slice, clipped to numel
+    end: int = 0
+    bf16: Optional[torch.Tensor] = None  # full layer, bf16, padded to shard * world: all-gather target
+
+
+class _RawCuda:
+    """Wraps a raw device pointer for torch.as_tensor (zero copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class ControlPlane:
+    """Host-side agreement between ranks over gloo: identical-spec checks and error flags.
+    Works on CPU-only hosts (it is what the world_size-2 CPU tests exercise)."""
+
+    def __init__(self, timeout_seconds: float = 120):
+        if not dist.is_initialized():
+            raise RuntimeError("Initialize torch.distributed before SharedDataParallel")
+        self.rank = dist.get_rank()
+        self.world_size = dist.get_world_size()
+        self.group = dist.new_group(backend="gloo", timeout=timedelta(seconds=timeout_seconds))
+
+    def all_same(self, spec) -> bool:
+        specs = [None] * self.world_size
+        dist.all_gather_object(specs, spec, group=self.group)
+        return len(set(specs)) == 1
+
+    def gather(self, obj) -> list:
+        out = [None] * self.world_size
+        dist.all_gather_object(out, obj, group=self.group)
+        return out
+
+    def any_failed(self, failed: bool) -> bool:
+        t = torch.tensor([1 if failed else 0], dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return bool(t.item())
+
+    def barrier(self):
+        dist.barrier(group=self.group)
+
+    def close(self):
+        dist.destroy_process_group(self.group)
+
+
+class SharedDataParallel:
+    """Collectively construct on all local ranks (after `init_process_group("nccl")` and
+    `torch.cuda.set_device`).  Call `reduce_chunk` / `fused_update` in identical layer and
+    chunk order on every rank."""
+
+    def __init__(self, chunk_numel=32 * 1024 * 1024, dtype=torch.bfloat16, shm_dir=None, timeout_seconds=120,
+                 *, device=None, exchange_slots: int = 2):
+        if not dist.is_initialized():
+            raise RuntimeError("Initialize torch.distributed before SharedDataParallel")
+        if chunk_numel < 1:
+            raise ValueError("chunk_numel must be positive")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("gradient dtype must be bfloat16 or float32")
+        if not torch.cuda.is_available():
+            raise RuntimeError("SharedDataParallel needs CUDA devices; there is no CPU data path")
+        self.ctl = ControlPlane(timeout_seconds)
+        self.rank, self.world_size = self.ctl.rank, self.ctl.world_size
+        if self.world_size > 16:
+            raise ValueError("at most 16 ranks")
+        self.chunk_numel = int(chunk_numel)
+        self.dtype = dtype
+        self.layers: Dict[int, LayerState] = {}
+        self.error = None
+        self._closed = False
+        self.directory = None  # the reference's /dev/shm directory has no counterpart
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._lib = _lib.load()
+        self._gcode = _lib.SF_GRAD_BF16 if dtype == torch.bfloat16 else _lib.SF_GRAD_F32
+        self._esize = 2 if dtype == torch.bfloat16 else 4
+        if not self.ctl.all_same((socket.gethostname(), self.chunk_numel, str(dtype), exchange_slots)):
+            raise ValueError("SharedDataParallel requires one host and matching chunk size/dtype")
+        self.exchange_slots = int(exchange_slots)
+        self._cap = 0                       # elements per exchange slot
+        self._base = None                   # local exchange allocation (raw pointer)
+        self._peer_base: List[int] = []     # every rank's exchange base mapped here (own = local pointer)
+        self._exchange: List[torch.Tensor] = []
+        self._mean: Optional[torch.Tensor] = None
+        self._token = torch.zeros(1, device=self.device)
+        self.group = self.ctl.group
+
+    # ---- exchange buffers ------------------------------------------------------------------
+    def _free_exchange(self):
+        for r, ptr in enumerate(self._peer_base):
+            if r != self.rank and ptr:
+                self._lib.sf_ipc_close(ptr)
+        self._peer_base = []
+        self._exchange = []
+        if self._base:
+            with torch.cuda.device(self.device):
+                _lib.check(self._lib.sf_dev_free(self._base))
+            self._base = None
+
+    def _grow_exchange(self, elems: int):
+        """Collective: (re)allocate the exchange slots for `elems` elements and map the peers'."""
+        if elems <= self._cap:
+            return
+        torch.cuda.synchronize(self.device)
+        self.ctl.barrier()
+        self._free_exchange()
+        elems = -(-elems // 128) * 128
+        nbytes = elems * self._esize * self.exchange_slots
+        with torch.cuda.device(self.device):
+            ptr = C.c_void_p()
+            _lib.check(self._lib.sf_dev_alloc(nbytes, C.byref(ptr)))
+            self._base = ptr.value
+            handle = (C.c_ubyte * _lib.SF_IPC_HANDLE_BYTES)()
+            _lib.check(self._lib.sf_ipc_export(self._base, handle))
+            handles = self.ctl.gather(bytes(handle))
+            self._peer_base = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self._peer_base.append(self._base)
+                    continue
+                buf = (C.c_ubyte * _lib.SF_IPC_HANDLE_BYTES).from_buffer_copy(h)
+                out = C.c_void_p()
+                _lib.check(self._lib.sf_ipc_open(buf, C.byref(out)))
+                self._peer_base.append(out.value)
+            flat = torch.as_tensor(_RawCuda(self._base, nbytes), device=self.device)
+            flat.zero_()
+            self._exchange = [flat[k * elems * self._esize:(k + 1) * elems * self._esize].view(self.dtype)
+                              for k in range(self.exchange_slots)]
+        self._cap = elems
+        torch.cuda.synchronize(self.device)
+        self.ctl.barrier()
+
+    def grad_buffer(self, slot: int = 0) -> torch.Tensor:
+        """This rank's exchange slot (dtype = self.dtype, capacity >= the largest registered layer).
+        Writing gradients straight into it saves the copy `reduce_chunk` would make."""
+        return self._exchange[slot]
+
+    def _peer_ptrs(self, slot: int, offset_elems: int):
+        arr = (C.c_void_p * self.world_size)()
+        for r in range(self.world_size):
+            arr[r] = self._peer_base[r] + (slot * self._cap + offset_elems) * self._esize
+        return arr
+
+    # ---- registration ----------------------------------------------------------------------
+    def register_layer(self, layer_idx, numel) -> LayerState:
+        if not self.ctl.all_same((layer_idx, int(numel))) or layer_idx in self.layers:
+            raise ValueError("Ranks must register identical layers exactly once")
+        numel = int(numel)
+        s = shard_numel(numel, self.world_size)
+        a, b = shard_range(numel, self.world_size, self.rank)
+        dev = self.device
+        state = LayerState(
+            params=torch.zeros(s, dtype=torch.float32, device=dev),
+            exp_avg=torch.zeros(s, dtype=torch.float32, device=dev),
+            exp_avg_sq=torch.zeros(s, dtype=torch.float32, device=dev),
+            numel=numel, shard=s, start=a, end=b,
+            bf16=torch.zeros(s * self.world_size, dtype=torch.bfloat16, device=dev))
+        self._grow_exchange(s * self.world_size)
+        self.layers[layer_idx] = state
+        return state
+
+    def load_full_params(self, layer_idx, full_fp32: torch.Tensor):
+        """Initialise this rank's slice (and the bf16 copy) from a full flat fp32 layer."""
+        st = self.layers[layer_idx]
+        st.params[: st.end - st.start].copy_(full_fp32[st.start:st.end])
+        st.bf16[: st.numel].copy_(full_fp32[: st.numel])
+
+    # ---- synchronisation ---------------------------------------------------------------------
+    def barrier(self):
+        """Host barrier over the control plane, like the reference's gloo barrier."""
+        self.ctl.barrier()
+
+    def stream_barrier(self):
+        """Orders the current CUDA stream after every rank's stream has reached this point."""
+        dist.all_reduce(self._token)
+
+    def raise_if_failed(self):
+        if self.error is not None:
+            raise RuntimeError("A distributed update failed") from self.error
+
+    def _validate(self, state, start, end, local_grad):
+        count = end - start
+        if not 0 <= start < end <= state.numel or count > self.chunk_numel:
+            raise ValueError("Invalid gradient chunk")
+        if local_grad is not None and (local_grad.device.type != "cuda" or local_grad.numel() != count
+                                       or local_grad.dtype != self.dtype):
+            raise ValueError("Gradient chunk must match the configured CUDA dtype and size")
+        return count
+
+    def _stage(self, slot, start, end, local_grad):
+        if local_grad is None:
+            return
+        dst = self._exchange[slot][start:end]
+        if local_grad.data_ptr() != dst.data_ptr():
+            dst.copy_(local_grad.view(-1))
+
+    # ---- the reference-shaped call -------------------------------------------------------------
+    @torch.no_grad()
+    def reduce_chunk(self, layer_idx, start, end, local_grad, update: Callable, slot: int = 0,
+                     check_errors: bool = True):
+        """Average a chunk over all ranks in fp32 (rank order) and hand each slice owner its part:
+        `update(params, mean_grad, exp_avg, exp_avg_sq)` receives fp32 device views of the
+        intersection of [start, end) with this rank's slice.  EVERY rank is called once per chunk,
+        with empty views when it owns nothing of the chunk: an optimizer whose scalars depend on
+        the call history (the reference's beta^t state machine does) then sees the same history
+        on every rank as the reference's rank 0.  On return the exchange slot region may be
+        overwritten (stream-ordered)."""
+        self.raise_if_failed()
+        state = self.layers[layer_idx]
+        self._validate(state, start, end, local_grad)
+        self._stage(slot, start, end, local_grad)
+        self.stream_barrier()
+        a, b = max(start, state.start), min(end, state.end)
+        failure = None
+        try:
+            k = max(b - a, 0)
+            if self._mean is None or self._mean.numel() < k:
+                self._mean = torch.empty(max(k, min(self.chunk_numel, state.shard)), dtype=torch.float32,
+                                         device=self.device)
+            mean = self._mean[:k]
+            if k > 0:
+                with torch.cuda.device(self.device):
+                    _lib.check(self._lib.sf_dp_mean(self._peer_ptrs(slot, a), self.world_size, self._gcode,
+                                                    mean.data_ptr(), k, torch.cuda.current_stream().cuda_stream))
+            lo = max(a - state.start, 0) if k > 0 else 0
+            update(state.params[lo:lo + k], mean, state.exp_avg[lo:lo + k], state.exp_avg_sq[lo:lo + k])
+        except Exception as exc:  # propagate to every rank below
+            failure = exc
+        if check_errors and self.ctl.any_failed(failure is not None):
+            self.error = failure if failure is not None else RuntimeError("a peer rank failed")
+            self.raise_if_failed()
+        elif failure is not None:
+            self.error = failure
+            self.raise_if_failed()
+        self.stream_barrier()
+
+    # ---- the fused call --------------------------------------------------------------------------
+    @torch.no_grad()
+    def fused_update(self, layer_idx, adam, param_group: dict, start: int = 0, end: Optional[int] = None,
+                     local_grad: Optional[torch.Tensor] = None, slot: int = 0, gather: bool = True):
+        """Mean + Adam + bf16 cast in one kernel on this rank's part of [start, end), then (by
+        default) the all-gather of the layer's bf16 weights.  `adam` is a LayerAdam (its scalar
+        state machine advances once per call, like one reference adam_update)."""
+        self.raise_if_failed()
+        state = self.layers[layer_idx]
+        end = state.numel if end is None else end
+        if state.numel == 0:
+            return
+        if not 0 <= start < end <= state.numel:
+            raise ValueError("Invalid gradient chunk")
+        if local_grad is not None:
+            self._validate(state, start, end, local_grad)
+            self._stage(slot, start, end, local_grad)
+        self.stream_barrier()
+        sc = _lib.SfAdamScalars()
+        _lib.check(self._lib.sf_adam_scalars(adam.optimizer_id, int(param_group["step"]), param_group["lr"],
+                                             param_group["betas"][0], param_group["betas"][1], param_group["eps"],
+                                             param_group["weight_decay"], int(param_group["bias_correction"] == 1),
+                                             C.byref(sc)))
+        a, b = max(start, state.start), min(end, state.end)
+        if b > a:
+            k, lo = b - a, a - state.start
+            vec_ref = start + ((end - start) & ~15)         # where the reference call's tail begins
+            vec_local = min(max(vec_ref - a, 0), k)
+            with torch.cuda.device(self.device):
+                _lib.check(self._lib.sf_adam_step_sharded(
+                    C.byref(sc), state.params[lo:lo + k].data_ptr(), self._peer_ptrs(slot, a), self.world_size,
+                    self._gcode, state.exp_avg[lo:lo + k].data_ptr(), state.exp_avg_sq[lo:lo + k].data_ptr(),
+                    state.bf16[a:b].data_ptr(), k, vec_local, torch.cuda.current_stream().cuda_stream))
+        if gather:
+            self.all_gather_params(layer_idx)
+
+    @torch.no_grad()
+    def all_gather_params(self, layer_idx, async_op: bool = False):
+        """All-gather the bf16 slices into every rank's full-layer buffer (in place).  Its
+        completion on a rank also means every rank has finished reading that rank's gradients."""
+        state = self.layers[layer_idx]
+        if state.shard == 0:
+            return None
+        mine = state.bf16[self.rank * state.shard:(self.rank + 1) * state.shard]
+        return dist.all_gather_into_tensor(state.bf16, mine, async_op=async_op)
+
+    # ---- NCCL-only variant (bf16 reduction, not bit-identical to the fp32 rank-order mean) --------
+    @torch.no_grad()
+    def nccl_update(self, layer_idx, adam, param_group: dict, slot: int = 0, gather: bool = True):
+        state = self.layers[layer_idx]
+        if state.numel == 0:
+            return
+        full = self._exchange[slot][: state.shard * self.world_size]
+        mine = full[self.rank * state.shard:(self.rank + 1) * state.shard]
+        dist.reduce_scatter_tensor(mine, full, op=dist.ReduceOp.AVG)
+        k = state.end - state.start
+        if k > 0:
+            adam.step_chunk(state.params[:k], mine[:k], state.exp_avg[:k], state.exp_avg_sq[:k], param_group,
+                            state.bf16[state.start:state.end])
+        if gather:
+            self.all_gather_params(layer_idx)
+
+    def close(self):
+        """Release local resources after all ranks have drained their work."""
+        if self._closed:
+            return
+        self._closed = True
+        torch.cuda.synchronize(self.device)
+        self.ctl.barrier()
+        self.layers.clear()
+        self._free_exchange()
+        self._cap = 0
+        self.ctl.close()
+
+
+class ShardedLayerAdam:
+    """One flat layer sharded over all ranks; the multi-GPU benchmark and the sweep drive this.
+
+    step(k): every rank's gradient buffer k -> fp32 rank-order mean + Adam on the owned slice
+    (mode "fused": one kernel reading the peers' buffers; mode "nccl": NCCL bf16 reduce-scatter,
+    then the single-GPU kernel) -> all-gather of the bf16 weights."""
+
+    def __init__(self, numel: int, device, mode: str = "fused", grad_slots: int = 3, **hp):
+        from .layer_adam import LayerAdam
+        if mode not in ("fused", "nccl"):
+            raise ValueError("mode must be 'fused' or 'nccl'")
+        self.mode = mode
+        self.dp = SharedDataParallel(chunk_numel=max(int(numel), 1), dtype=torch.bfloat16, device=device,
+                                     exchange_slots=grad_slots)
+        self.adam = LayerAdam(**hp)
+        self.state = self.dp.register_layer(0, numel)
+        self.numel = int(numel)
+        self.shard_numel = self.state.end - self.state.start
+        self.params_shard = self.state.params
+        self.group = dict(self.adam.defaults, step=0)
+
+    def grad_buffer(self, k: int) -> torch.Tensor:
+        return self.dp.grad_buffer(k)[: self.numel]
+
+    def describe(self) -> str:
+        if self.mode == "fused":
+            return "fused peer-read fp32 rank-order mean + Adam kernel over NVLink, NCCL bf16 all-gather"
+        return "NCCL bf16 reduce-scatter (avg), Adam kernel, NCCL bf16 all-gather"
+
+    def step(self, k: int = 0):
+        self.group["step"] += 1
+        if self.mode == "fused":
+            self.dp.fused_update(0, self.adam, self.group, slot=k)
+        else:
+            self.dp.nccl_update(0, self.adam, self.group, slot=k)
+
+    def close(self):
+        self.dp.close()

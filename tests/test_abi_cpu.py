@@ -114,7 +114,7 @@ def test_error_codes_without_gpu(lib):
                                    0, 24, 0, None, 0, None) == _lib.SF_ERR_ARG  # chunk not a multiple of 16
     assert lib.sf_adam_host_scratch_bytes(1024, 0, 1) == 2 * (3 * 4096 + 2048)
     assert lib.sf_adam_host_scratch_bytes(1024, 0, 0) == 2 * (3 * 4096)
-    assert lib.sf_set_tuning(7, 0) == _lib.SF_ERR_ARG
+    assert lib.sf_set_tuning(7, -1) == _lib.SF_ERR_ARG
     assert lib.sf_adam_destroy(77) == 0
     assert lib.sf_adam_destroy(77) == 0  # unknown ids are ignored
 

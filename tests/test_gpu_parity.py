@@ -54,7 +54,7 @@ def assert_bits(got: torch.Tensor, want: np.ndarray, what=""):
 @pytest.mark.parametrize("name", sorted(TRAJ_CASES))
 def test_golden_trajectories(name, variant, golden, lib):
     from slideformer_b200 import LayerAdam
-    lib.sf_set_tuning(variant, 0)
+    lib.sf_set_tuning(variant, -1)
     try:
         hp, adamw, bc, steps = TRAJ_CASES[name]
         p = torch.from_numpy(golden[f"{name}/p0"].copy()).to(DEV)
@@ -80,7 +80,7 @@ def test_golden_trajectories(name, variant, golden, lib):
                 assert_bits(v, golden[f"{tag}/v"], f"{tag} v")
                 assert_bits(out, golden[f"{tag}/bf16"], f"{tag} bf16")
     finally:
-        lib.sf_set_tuning(1, 0)
+        lib.sf_set_tuning(1, -1)
 
 
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
@@ -184,9 +184,19 @@ REFHP = (0.01, 0.8, 0.95, 1e-6, 0.1)
 @pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("n", [4, 7, 8, 31, 2047, 2048, 2049, 4096 + 16, (1 << 20) + 13, 3 * (1 << 20)])
 def test_sizes_vs_oracle(n, variant, oracle, lib):
-    lib.sf_set_tuning(variant, 0)
+    lib.sf_set_tuning(variant, -1)
     try:
         compare(*run_both(oracle, lib, n, 3, CFG0, seed=n))
+    finally:
+        lib.sf_set_tuning(1, -1)
+
+
+@pytest.mark.parametrize("ctas_per_sm", [1, 8])
+def test_persistent_grid_vs_oracle(ctas_per_sm, oracle, lib):
+    """The tile-walking (persistent) launch shape gives the same bits as one tile per CTA."""
+    lib.sf_set_tuning(1, ctas_per_sm)
+    try:
+        compare(*run_both(oracle, lib, 3 * (1 << 20) + 5, 2, CFG0, seed=77))
     finally:
         lib.sf_set_tuning(1, 0)
 
@@ -202,22 +212,22 @@ def test_sizes_vs_oracle(n, variant, oracle, lib):
     (False, False, 0.0, torch.float32, True),
 ])
 def test_modes_vs_oracle(adamw, bc, wd, gdtype, with_out, variant, oracle, lib):
-    lib.sf_set_tuning(variant, 0)
+    lib.sf_set_tuning(variant, -1)
     try:
         hp = (REFHP[0], REFHP[1], REFHP[2], REFHP[3], wd)
         compare(*run_both(oracle, lib, 70001, 4, hp, adamw, bc, gdtype, with_out, seed=11))
     finally:
-        lib.sf_set_tuning(1, 0)
+        lib.sf_set_tuning(1, -1)
 
 
 @pytest.mark.parametrize("variant", [0, 1, 2])
 def test_special_values(variant, oracle, lib):
     """Zeros, signed zero, infinities, subnormals, huge values; NaN results compare as NaN."""
-    lib.sf_set_tuning(variant, 0)
+    lib.sf_set_tuning(variant, -1)
     try:
         compare(*run_both(oracle, lib, 4096, 3, CFG0, special=True, seed=5), allow_nan=True)
     finally:
-        lib.sf_set_tuning(1, 0)
+        lib.sf_set_tuning(1, -1)
 
 
 def test_misaligned_slices_take_the_scalar_kernel(oracle, lib):
@@ -404,7 +414,7 @@ def test_full_layer_properties(oracle, lib):
     g = (torch.randn(n, device=DEV, generator=gen) * 1e-3).to(torch.bfloat16)
     results = []
     for variant in (0, 1, 2):
-        lib.sf_set_tuning(variant, 0)
+        lib.sf_set_tuning(variant, -1)
         p, m, v = p0.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
         out = torch.empty(n, device=DEV, dtype=torch.bfloat16)
         opt = LayerAdam(lr=CFG0[0], betas=CFG0[1:3], eps=CFG0[3], weight_decay=CFG0[4])
@@ -412,7 +422,7 @@ def test_full_layer_properties(oracle, lib):
             opt.step_chunk(p, g, m, v, dict(opt.defaults, step=step), out)
         torch.cuda.synchronize()
         results.append((p, m, v, out))
-    lib.sf_set_tuning(1, 0)
+    lib.sf_set_tuning(1, -1)
     # (1) the three access patterns agree on every bit of every output
     for other in results[1:]:
         for a, b in zip(results[0], other):
