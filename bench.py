@@ -37,9 +37,12 @@ HP = dict(lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
 WORKLOAD = "llama3.1-8b decoder layer, flat n=218112000, fp32 p/m/v + bf16 grad -> bf16 copy"
 METRIC = "LayerAdam Gparams/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch at n = 218,112,000, scaled by n
-# from the ncu capture summarised in profiles/ (bytes per parameter); None until captured.
-NCU_TRAFFIC_BYTES_PER_PARAM = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
+# profiles/adam_vec4_kernel_llama8b_layer.md (n = 16,777,216): reads are 14.00 B/param, writes
+# are 14 B/param minus about 56 MB that is still dirty in L2 when the kernel ends (a constant,
+# it does not grow with n).  Scaled to a launch over `units` parameters.
+def ncu_traffic_bytes(units: int) -> float:
+    return 14.0 * units + max(14.0 * units - 56e6, 0.0)
 
 
 def measured_peak():
@@ -314,7 +317,7 @@ def main_b200(args):
     achieved = hbm_bytes_per_launch / (kern_ms * 1e-3) / 1e9
     units = n if world == 1 else sh.shard_numel
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": (NCU_TRAFFIC_BYTES_PER_PARAM * units) if NCU_TRAFFIC_BYTES_PER_PARAM else None,
+                "traffic": ncu_traffic_bytes(units) if world == 1 else None,
                 "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs, burst copy)" if which == "measured" else "fallback 6650 GB/s",
                 "kernel": "adam_vec4_kernel", "kernel_ms": kern_ms, "bytes_per_launch": hbm_bytes_per_launch,
                 "frac_of_nominal_8000": achieved / 8000.0}
@@ -366,7 +369,7 @@ def main_b200(args):
                                        "path": "sf_adam_update_host: p, m, v, g in pinned host memory, double-buffered chunks"}
             del ph, mh, vh
     else:
-        e2e = sh.e2e(args, K)
+        e2e = sh.e2e(K)
     sampler.stop()
 
     cpu_baseline = None

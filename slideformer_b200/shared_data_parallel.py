@@ -410,5 +410,82 @@ class ShardedLayerAdam:
         else:
             self.dp.nccl_update(0, self.adam, self.group, slot=k)
 
+    # ---- measurement helpers (device-timed with CUDA events on the launching stream) -------------
+    def _timed(self, fn, reps: int) -> float:
+        fn()
+        torch.cuda.synchronize(self.dp.device)
+        self.dp.ctl.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize(self.dp.device)
+        t = torch.tensor([a.elapsed_time(b) / reps], device=self.dp.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def time_kernel_only(self, reps: int) -> float:
+        """Average duration (ms, max over ranks) of the Adam kernel alone on the owned slice: in
+        fused mode it includes the peer gradient reads over NVLink, but no barrier or all-gather."""
+        st, dp = self.state, self.dp
+        k = st.end - st.start
+
+        def fused():
+            self.group["step"] += 1
+            sc = _lib.SfAdamScalars()
+            g = self.group
+            _lib.check(dp._lib.sf_adam_scalars(self.adam.optimizer_id, g["step"], g["lr"], g["betas"][0], g["betas"][1],
+                                               g["eps"], g["weight_decay"], int(g["bias_correction"] == 1), C.byref(sc)))
+            if k > 0:
+                _lib.check(dp._lib.sf_adam_step_sharded(
+                    C.byref(sc), st.params.data_ptr(), dp._peer_ptrs(0, st.start), dp.world_size, dp._gcode,
+                    st.exp_avg.data_ptr(), st.exp_avg_sq.data_ptr(), st.bf16[st.start:st.end].data_ptr(), k, k,
+                    torch.cuda.current_stream().cuda_stream))
+
+        def local():
+            self.group["step"] += 1
+            mine = dp._exchange[0][dp.rank * st.shard: dp.rank * st.shard + k]
+            self.adam.step_chunk(st.params[:k], mine, st.exp_avg[:k], st.exp_avg_sq[:k], self.group,
+                                 st.bf16[st.start:st.end])
+
+        return self._timed(fused if self.mode == "fused" else local, reps)
+
+    def breakdown(self, reps: int) -> dict:
+        """Separate device times (ms, max over ranks) of the collectives around the kernel."""
+        st, dp = self.state, self.dp
+        out = {"stream_barrier_ms": self._timed(dp.stream_barrier, reps),
+               "all_gather_bf16_ms": self._timed(lambda: dp.all_gather_params(0), reps)}
+        if self.mode == "nccl":
+            full = dp._exchange[0][: st.shard * dp.world_size]
+            mine = full[dp.rank * st.shard:(dp.rank + 1) * st.shard]
+            out["reduce_scatter_bf16_ms"] = self._timed(
+                lambda: dist.reduce_scatter_tensor(mine, full, op=dist.ReduceOp.AVG), reps)
+        sent = 2 * st.shard * (dp.world_size - 1)
+        out["all_gather_bus_gbs_per_gpu"] = sent / (out["all_gather_bf16_ms"] * 1e-3) / 1e9
+        return {"dp_breakdown": out}
+
+    def e2e(self, steps: int) -> dict:
+        """The same step with host buffers: every rank uploads its pinned bf16 gradient into the
+        exchange slot and downloads the bf16 copy of its updated slice, inside the timed region."""
+        st, dp = self.state, self.dp
+        n, k = self.numel, st.end - st.start
+        g_host = torch.empty(n, dtype=torch.bfloat16).pin_memory()
+        g_host.copy_(dp.grad_buffer(0)[:n])
+        out_host = torch.empty(max(k, 1), dtype=torch.bfloat16).pin_memory()
+
+        def one():
+            dp.grad_buffer(0)[:n].copy_(g_host, non_blocking=True)
+            self.step(0)
+            if k > 0:
+                out_host[:k].copy_(st.bf16[st.start:st.end], non_blocking=True)
+
+        for _ in range(2):
+            one()
+        ms = self._timed(one, max(3, min(steps, 20)))
+        return {"value": n / (ms * 1e-3) / 1e9, "unit": "Gparams/s", "ms_per_step": ms,
+                "h2d_bytes_per_step": 2 * n * dp.world_size, "d2h_bytes_per_step": 2 * n,
+                "path": "every rank: pinned bf16 gradient -> exchange slot, ShardedLayerAdam.step, bf16 slice -> pinned host"}
+
     def close(self):
         self.dp.close()
