@@ -123,6 +123,33 @@ int sf_adam_step_sharded(const SfAdamScalars* s, float* p, const void* const* pe
  * in fp32, rank order.  mean is a local fp32[n] device buffer. */
 int sf_dp_mean(const void* const* peer_g, int world, int g_dtype, float* mean, uint64_t n, void* stream);
 
+/* No counterpart in the reference.  Same result as sf_dp_mean into a caller buffer followed by
+ * sf_adam_update on that fp32 mean, but the mean is staged in memory that is part of the
+ * library image, so the call performs no device allocation of any kind.
+ *
+ * Who needs this: code that runs once the training step is in steady state, typically the
+ * per-chunk gradient reduction on the optimizer thread in the middle of backward.  By then the
+ * HBM budget is fully handed out (fp32 state, the layer window, activations), so a cudaMalloc
+ * can fail, and even when it succeeds it stalls the device that the main thread is feeding
+ * with kernels.  Such callers cannot allocate a staging buffer, and may not own one.
+ *
+ * Limit: n <= sf_static_scratch_max_elems() (4 Mi elements, a 16 MiB fp32 array that every GPU
+ * using the library holds until the process exits); larger n is rejected with SF_ERR_SIZE
+ * before anything runs -- split the range into several calls.
+ *
+ * The first call on each device looks up the array's device address (with that device
+ * current) and remembers it; make that first call before starting any stream capture.
+ * All calls on a device share the one array and it keeps whatever the last call left there.
+ * Nothing has to be cleared between calls because each call rewrites mean[0, n) before reading
+ * it, but two calls that can run at the same time on the GPU (different streams, no ordering)
+ * race on it: keep calls on one device ordered.  Other arguments as for sf_dp_mean and
+ * sf_adam_update. */
+uint64_t sf_static_scratch_max_elems(void);
+int sf_adam_update_dp_static(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
+                             float weight_decay, int bias_correction, float* p,
+                             const void* const* peer_g, int world, int g_dtype, float* m, float* v,
+                             uint16_t* p_bf16, uint64_t n, void* stream);
+
 /* ---- the fused step for host-resident state -------------------------------------------- */
 
 /* For optimizer state that does not fit in HBM: p, m, v live in PINNED host memory (the

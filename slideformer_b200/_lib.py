@@ -46,6 +46,9 @@ SIGNATURES = {
     "sf_adam_step_sharded": (_i, [C.POINTER(SfAdamScalars), _vp, C.POINTER(_vp), _i, _i, _vp, _vp, _vp,
                                   _u64, _u64, _vp]),
     "sf_dp_mean": (_i, [C.POINTER(_vp), _i, _i, _vp, _u64, _vp]),
+    "sf_static_scratch_max_elems": (_u64, []),
+    "sf_adam_update_dp_static": (_i, [_i, _u64, _f, _f, _f, _f, _f, _i, _vp, C.POINTER(_vp), _i, _i, _vp, _vp, _vp,
+                                      _u64, _vp]),
     "sf_adam_host_scratch_bytes": (C.c_size_t, [_u64, _i, _i]),
     "sf_adam_update_host": (_i, [_i, _u64, _f, _f, _f, _f, _f, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _u64,
                                  _u64, _i, _vp, C.c_size_t, _vp]),

@@ -651,6 +651,32 @@ int get_pipe(HostPipe** out)
 
 size_t round256(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// ---- scratch for the entry point that must not allocate ------------------------------------
+// Reserved in the library image itself: every GPU that loads the library carries these 16 MiB
+// until the process exits.  The name below is only a handle on the host; the device address
+// comes from cudaGetSymbolAddress, once per device, with that device current.
+constexpr uint64_t kStaticMeanMaxElems = (uint64_t)4 << 20;  // 4 Mi fp32 values = 16 MiB
+static __device__ __align__(256) float g_static_mean[kStaticMeanMaxElems];
+
+std::mutex g_static_mu;
+std::unordered_map<int, float*> g_static_addr;  // device ordinal -> device address of g_static_mean
+
+int static_mean_address(float** out)
+{
+    int dev = 0;
+    SF_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    auto it = g_static_addr.find(dev);
+    if (it == g_static_addr.end()) {
+        float* ptr = nullptr;
+        SF_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_mean));
+        if (!ptr) return fail(SF_ERR_CUDA, "cudaGetSymbolAddress returned a NULL address for the static scratch");
+        it = g_static_addr.emplace(dev, ptr).first;
+    }
+    *out = it->second;
+    return SF_OK;
+}
+
 }  // namespace
 
 // ==========================================================================================
@@ -795,6 +821,27 @@ int sf_dp_mean(const void* const* peer_g, int world, int g_dtype, float* mean, u
         dp_mean_kernel<<<grid, 256, 0, st>>>(gs, mean, nvec, n);
     }
     return check_launch("dp_mean_kernel");
+}
+
+uint64_t sf_static_scratch_max_elems(void) { return kStaticMeanMaxElems; }
+
+int sf_adam_update_dp_static(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
+                             float weight_decay, int bias_correction, float* p,
+                             const void* const* peer_g, int world, int g_dtype, float* m, float* v,
+                             uint16_t* p_bf16, uint64_t n, void* stream)
+{
+    if (n > kStaticMeanMaxElems)
+        return fail(SF_ERR_SIZE, "n = " + std::to_string(n) + " exceeds the built-in scratch of " +
+                                     std::to_string(kStaticMeanMaxElems) +
+                                     " elements; split the call or use sf_dp_mean + sf_adam_update with your own buffer");
+    if (n > 0 && (!p || !m || !v)) return fail(SF_ERR_NULL, "p, m and v must be non-NULL when n > 0");
+    float* mean = nullptr;
+    if (int rc = static_mean_address(&mean)) return rc;
+    // mean[0, n) is fully rewritten by the first kernel before the second reads it, so nothing
+    // left over from an earlier call is ever consumed and nothing needs clearing.
+    if (int rc = sf_dp_mean(peer_g, world, g_dtype, mean, n, stream)) return rc;
+    return sf_adam_update(id, step, lr, beta1, beta2, eps, weight_decay, bias_correction, p, mean,
+                          SF_GRAD_F32, m, v, p_bf16, n, stream);
 }
 
 size_t sf_adam_host_scratch_bytes(uint64_t chunk_elems, int g_dtype, int g_on_host)
