@@ -1,0 +1,140 @@
+"""Fine-tune throughput of the layer-sliding engine on a random-init model (tokens/s).
+
+    python -m slideformer_b200.finetune_bench --model gpt2-small --batch 8 --seq 1024
+    python -m slideformer_b200.finetune_bench --model llama3.1-8b --batch 8 --seq 1024 [--state-device host]
+    torchrun --nproc-per-node N -m slideformer_b200.finetune_bench --model gpt2-small --dp     # sharded state
+
+Counterpart of the reference's scripts/main_bench.py measurement loop (warm-up steps, timed
+steps, tokens/s and TFLOPS by the Megatron formula of utils/metric.py:4-57) on synthetic data:
+token ids uniform in [0, vocab), labels = inputs (the engine shifts them).  Every step uploads
+its batch from pinned host memory and downloads the loss, inside the timed region.
+Prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+
+def model_flops_per_step(cfg, batch, seq):
+    """Forward + backward FLOPs of one step, dense decoder (utils/metric.py:4-57); 3x forward,
+    without the recompute of activation checkpointing."""
+    if getattr(cfg, "model_type", "") == "gpt2":
+        h, L, V, inter, heads, kv = cfg.n_embd, cfg.n_layer, cfg.vocab_size, 4 * cfg.n_embd, cfg.n_head, cfg.n_head
+        gated = 1.0
+    else:
+        h, L, V, inter = cfg.hidden_size, cfg.num_hidden_layers, cfg.vocab_size, cfg.intermediate_size
+        heads, kv = cfg.num_attention_heads, cfg.num_key_value_heads
+        gated = 1.5
+    return 12 * batch * seq * L * h * h * ((1 + kv / heads + seq / h) + (inter / h) * gated + V / (2 * L * h))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="gpt2-small")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=None, help="override the number of decoder layers")
+    ap.add_argument("--state-device", default="hbm", choices=["hbm", "host"])
+    ap.add_argument("--activation-offload", default="hbm", choices=["hbm", "host"])
+    ap.add_argument("--no-ckpt", action="store_true", help="keep all activations instead of checkpointing each layer")
+    ap.add_argument("--double-buffer", action="store_true")
+    ap.add_argument("--dp", action="store_true", help="shard optimizer state over all ranks (launch with torchrun)")
+    ap.add_argument("--lr", type=float, default=1e-5)
+    args = ap.parse_args(argv)
+
+    from slideformer_b200 import _lib
+    from slideformer_b200.model_compat import build_random_model
+    from slideformer_b200.offload_transformer import SlideFormerOffloader
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dp = None
+    if args.dp or world > 1:
+        import torch.distributed as dist
+        from slideformer_b200.shared_data_parallel import SharedDataParallel
+        dist.init_process_group("nccl", device_id=dev)
+        dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=3 if args.double_buffer else 2)
+    lib = _lib.load()
+
+    t_build = time.perf_counter()
+    model = build_random_model(args.model, dev, torch.bfloat16, seed=0, num_layers=args.layers)
+    engine = SlideFormerOffloader(
+        model, dev, torch.bfloat16, double_buffer=args.double_buffer, enable_timing=True, enable_memory_stats=False,
+        optimizer_kwargs=dict(lr=args.lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01),
+        shared_dp=dp, state_device=args.state_device, activation_offload=args.activation_offload,
+        activation_checkpoint=not args.no_ckpt)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t_build
+
+    vocab = model.config.vocab_size
+    gen = torch.Generator().manual_seed(1234 + rank)
+    nb = 4
+    host_ids = [torch.randint(0, vocab, (args.batch, args.seq), generator=gen).pin_memory() for _ in range(nb)]
+    loss_host = torch.zeros(1).pin_memory()
+
+    def step(i):
+        ids = host_ids[i % nb].to(dev, non_blocking=True)
+        out = engine(ids, labels=ids)
+        loss_host.copy_(out.loss.detach().float().reshape(1), non_blocking=True)
+        return out
+
+    losses = []
+    for i in range(args.warmup):
+        step(i)
+        torch.cuda.synchronize()
+        losses.append(float(loss_host.item()))
+    if dp is not None:
+        dp.barrier()
+    torch.cuda.synchronize()
+    l0 = lib.sf_launch_count()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    a.record()
+    for i in range(args.steps):
+        step(i)
+    b.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    losses.append(float(loss_host.item()))
+    ms = max(a.elapsed_time(b), wall * 1e3) / args.steps
+    if dp is not None:
+        t = torch.tensor([ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    tokens = args.batch * args.seq * world
+    upd = engine.parameter_update_ms()
+    flops = model_flops_per_step(model.config, args.batch, args.seq) * world
+    line = {"metric": "fine-tune tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.model} full fine-tune, layer sliding", "global_batch": args.batch * world,
+                       "seq_len": args.seq, "state_device": args.state_device,
+                       "activation_offload": args.activation_offload, "activation_checkpoint": not args.no_ckpt,
+                       "parallelism": f"dp{world} sharded state" if dp is not None else "single GPU"},
+            "model_tflops": flops / (ms * 1e-3) / 1e12, "params": sum(u.total_size for u in engine.transformer_layers),
+            "optimizer_ms_per_step": sum(upd.values()), "optimizer_ms_decoder_layer": upd.get(1),
+            "gpu_launches": int(lib.sf_launch_count() - l0), "loss_first": losses[0] if losses else None,
+            "loss_last": losses[-1], "build_seconds": build_s,
+            "max_memory_gb": torch.cuda.max_memory_allocated() / 2**30,
+            "e2e": {"h2d_bytes_per_step": args.batch * args.seq * 8 * world, "d2h_bytes_per_step": 4 * world}}
+    if rank == 0:
+        print(json.dumps(line))
+    if dp is not None:
+        dp.close()
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,192 @@
+"""SlideFormerOffloader: the layer-sliding fine-tuning engine around the GPU LayerAdam.
+
+Counterpart of the reference's offload_transformer.py:28-597 (and of its data-parallel copy,
+multi_gpu/offload_transformer.py): same constructor keywords, `forward(input_ids,
+attention_mask, labels, position_ids, return_dict)`, `wait_for_completion()`,
+`update_learning_rate()`, `save_pretrained()`.
+
+Schedule of one step (all ordering by CUDA events, no worker threads):
+
+  forward   unit i: compute stream waits for unit i's last optimizer step (`update_done`), runs
+            the layer on the permanent bf16 weights; decoder layers keep one checkpoint tensor
+            (in HBM, or in pinned host memory through `SlidingCheckpoint`).
+  backward  unit i, pre-hook: take a gradient unit from the ring (wait for its `reuse_ready`),
+            zero it, point .grad views into it.  When the last parameter of the unit has
+            accumulated its gradient, `compute_ready_bw` is recorded and the optimizer stream
+            runs the fused Adam kernel over the unit (fp32 p/m/v in place, bf16 weights out),
+            overlapping with the backward of unit i-1 on the compute stream.
+
+The reference's `double_buffer` selects 2 instead of 1 spare window units
+(offload_transformer.py:75-79); here it selects 3 instead of 2 gradient units.
+"""
+from __future__ import annotations
+
+import time
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .layer_adam import LayerAdam
+from .model_compat import parameter_sizes, prepare_layer_inputs, validate_model
+from .sliding_checkpoint import ActivationStore
+from .transformer_layer import GradUnitPool, split_transformer_model
+
+
+class CausalLMOutput(dict):
+    """Minimal stand-in for transformers' CausalLMOutputWithPast (attribute and key access)."""
+
+    def __getattr__(self, k):
+        try:
+            return self[k]
+        except KeyError as e:
+            raise AttributeError(k) from e
+
+
+class SlideFormerOffloader(nn.Module):
+    def __init__(self, model, device: torch.device, dtype: torch.dtype = torch.bfloat16, ac_offload_nvme: bool = False,
+                 offload_dir: str = "/RAID0", double_buffer: bool = False, enable_timing: bool = True,
+                 enable_memory_stats: bool = True, optimizer_kwargs: Optional[dict] = None,
+                 auto_backward_in_forward: bool = True, shared_dp=None, *, state_device: str = "hbm",
+                 activation_offload: str = "hbm", activation_checkpoint: bool = True, loss_chunk_tokens: int = 4096,
+                 update_chunk: Optional[int] = None):
+        super().__init__()
+        if not isinstance(device, torch.device):
+            raise TypeError("device must be torch.device")
+        if dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("dtype must be float16 or bfloat16")
+        if dtype != torch.bfloat16:
+            raise NotImplementedError("the fused optimizer emits bfloat16 weights; float16 is not supported")
+        if ac_offload_nvme:
+            raise NotImplementedError("NVMe activation offload is not part of this build; use activation_offload='host'")
+        if activation_offload not in ("hbm", "host"):
+            raise ValueError("activation_offload must be 'hbm' or 'host'")
+        self.device, self.dtype = device, dtype
+        self.double_buffer = double_buffer
+        self.auto_backward_in_forward = auto_backward_in_forward
+        self.enable_timing = enable_timing
+        self.enable_memory_stats = enable_memory_stats
+        self.shared_dp = shared_dp
+        self.state_device = state_device
+        self.activation_offload = activation_offload
+        self.base_model = model
+        self.parts = validate_model(model)
+        self.config = self.parts.config
+        self.decoder_layers = self.parts.layers
+        self.max_param_size, self.total_param = parameter_sizes(model)
+        self.is_tied = self.parts.tied_param is not None
+        self.tied_param = self.parts.tied_param
+
+        defaults = {"lr": 1e-5, "bias_correction": True, "weight_decay": 0.01, "eps": 1e-8,
+                    "fp32_optimizer_state": True, "num_layer": len(self.decoder_layers) + 2}
+        self.layer_optimizer = LayerAdam(**(optimizer_kwargs or defaults))
+
+        with torch.cuda.device(device):
+            self.opt_stream = torch.cuda.Stream()
+        n_units = min(3 if double_buffer else 2, len(self.decoder_layers) + 2)
+        self.gpu_unit_size = n_units
+        if shared_dp is not None:
+            if shared_dp.exchange_slots < n_units:
+                raise ValueError(f"shared_dp needs at least {n_units} exchange slots")
+            shared_dp._grow_exchange(-(-self.max_param_size // (16 * shared_dp.world_size)) * 16 * shared_dp.world_size)
+        self._grad_pool = None  # built after the layers registered (the exchange buffers may grow)
+
+        kwargs = dict(opt_stream=self.opt_stream, enable_timing=enable_timing, layer_optimizer=self.layer_optimizer,
+                      state_device=state_device, shared_dp=shared_dp, activation_checkpoint=activation_checkpoint,
+                      loss_chunk_tokens=loss_chunk_tokens)
+        if update_chunk is not None:
+            kwargs["update_chunk"] = update_chunk
+        comps = split_transformer_model(self.parts, device, dtype, **kwargs)
+        self.transformer_layers = comps["transformer_layers"]
+        self.rotary_emb = comps["rotary_emb"]
+        self.embed_layer = self.transformer_layers[0]
+        self.output_layer = self.transformer_layers[-1]
+
+        buffers = None
+        if shared_dp is not None:
+            buffers = [shared_dp.grad_buffer(k) for k in range(n_units)]
+        self._grad_pool = GradUnitPool(n_units, self.max_param_size, dtype, device, buffers)
+        for u in self.transformer_layers:
+            u.grad_pool = self._grad_pool
+
+        self.activation_store = None
+        self._activation_layout_signature = None
+        self._register_layer_hooks()
+        self.last_step_seconds = None
+
+    # ---- hooks (offload_transformer.py:221-308) ---------------------------------------------------
+    def _register_layer_hooks(self):
+        def pre_forward(module, args):
+            module.wait_for_update()
+            return None
+
+        def pre_backward(module, grad_output):
+            module.to_device_async(is_bwd=True)
+            return None
+
+        for unit in self.transformer_layers:
+            unit.register_forward_pre_hook(pre_forward)
+            unit.register_full_backward_pre_hook(pre_backward)
+
+    def wait_for_completion(self) -> None:
+        """Drain the step: flush units whose backward left parameters untouched, make the compute
+        stream wait for the optimizer stream, and synchronise (offload_transformer.py:326-335)."""
+        for unit in self.transformer_layers:
+            unit.flush()
+        torch.cuda.current_stream(self.device).wait_stream(self.opt_stream)
+        torch.cuda.synchronize(self.device)
+
+    def _ensure_activation_storage(self, batch_size, seq_length, hidden_size):
+        if self.activation_offload != "host":
+            return
+        sig = (batch_size, seq_length, hidden_size)
+        if self._activation_layout_signature == sig:
+            self.activation_store.reset()
+            return
+        self.activation_store = ActivationStore(len(self.decoder_layers), sig, self.dtype, self.device)
+        for unit in self.transformer_layers[1:-1]:
+            unit.activation_store = self.activation_store
+        self._activation_layout_signature = sig
+
+    def forward(self, input_ids, attention_mask=None, labels=None, position_ids=None, return_dict=None):
+        return_dict = True if return_dict is None else return_dict
+        t0 = time.perf_counter()
+        if self.parts.kind == "gpt2":
+            hidden = self.embed_layer(input_ids, position_ids=position_ids)
+        else:
+            hidden = self.embed_layer(input_ids)
+        layer_inputs = prepare_layer_inputs(self.parts, hidden, attention_mask, position_ids)
+        self._ensure_activation_storage(hidden.shape[0], hidden.shape[1], hidden.shape[2])
+        for idx in range(1, len(self.transformer_layers) - 1):
+            hidden = self.transformer_layers[idx](hidden, **layer_inputs[idx - 1])
+        loss = logits = None
+        if labels is not None:
+            loss = self.output_layer(hidden, labels=labels)
+            if self.auto_backward_in_forward:
+                loss.backward()
+                self.wait_for_completion()
+                self.last_step_seconds = time.perf_counter() - t0
+        else:
+            logits = self.output_layer(hidden, labels=None)
+        if not return_dict:
+            return tuple(v for v in (loss, logits) if v is not None)
+        return CausalLMOutput(loss=loss, logits=logits, past_key_values=None)
+
+    def update_learning_rate(self, new_lr):
+        self.layer_optimizer.update_learning_rate(new_lr)
+
+    def parameter_update_ms(self):
+        """Per-unit mean device time of the optimizer step (needs enable_timing)."""
+        out = {}
+        for u in self.transformer_layers:
+            spans = u.timings["parameter_update"]
+            if spans:
+                out[u.layer_idx] = sum(a.elapsed_time(b) for a, b in spans) / len(spans)
+        return out
+
+    def save_pretrained(self, output_dir):
+        """Write HF-format weights cast to the compute dtype (offload_transformer.py:593-597).  The
+        live parameters already are the bf16 weights, so the model saves itself."""
+        self.wait_for_completion()
+        self.base_model.save_pretrained(output_dir)
+        return output_dir

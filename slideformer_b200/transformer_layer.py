@@ -1,0 +1,347 @@
+"""Layer units of the sliding runtime, rescheduled around the fused GPU optimizer step.
+
+Counterpart of the reference's transformer_layer.py (`OffloadLayerWrapper`, `DecoderWrapper`,
+`EmbeddingWrapper`, `OutputWrapper`, `split_transformer_model`).  Public methods keep their
+names; what they do changes because the optimizer now runs on the GPU:
+
+  reference (CPU optimizer)                              here (B200)
+  ----------------------------------------------------   -----------------------------------------
+  fp32 master weights in CPU RAM, transformer_layer.py   fp32 master weights + Adam moments in HBM
+    :192-196; moments in CPU RAM, layer_adam.py:163-173    (or pinned host memory, streamed)
+  to_device_async: CPU fp32->bf16 cast + H2D into a      bf16 weights are permanent in HBM, written by
+    window unit on a worker thread, :273-335               the Adam kernel's epilogue; to_device_async
+                                                           only takes a gradient unit for backward
+  to_offload_async(is_bwd): chunked gradient D2H with    nothing to copy; the gradient unit is handed to
+    one event per chunk, :343-422                          the optimizer stream by an event
+  update_params: CPU thread consuming chunks, :453-499   one kernel launch per chunk on the optimizer
+                                                           stream (or the data-parallel fused update)
+  wait_for_update: threading.Event                       a CUDA event the compute stream waits on
+
+No Python worker threads are involved; every dependency is a CUDA event, so the host never
+blocks inside a step.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from .model_compat import TextModelParts, call_decoder_layer
+from .sliding_checkpoint import SlidingCheckpoint
+
+# Optimizer chunk, in elements: the reference's D2H chunk (transformer_layer.py:26-27).
+UPDATE_CHUNK_SIZE = 32 * 1024 * 1024
+
+
+class GradUnitPool:
+    """The gradient side of the reference's GPU cache units (offload_transformer.py:205-219):
+    a small ring of flat bf16 buffers, each guarded by a `reuse_ready` event recorded when the
+    optimizer has consumed it."""
+
+    def __init__(self, num_units: int, numel: int, dtype, device, buffers: Optional[List[torch.Tensor]] = None):
+        self.units = []
+        for k in range(num_units):
+            grad = buffers[k] if buffers is not None else torch.empty(numel, dtype=dtype, device=device)
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(device))
+            self.units.append({"grad": grad, "reuse_ready": ev, "slot": k})
+        self._next = 0
+
+    def get(self):
+        u = self.units[self._next % len(self.units)]
+        self._next += 1
+        return u
+
+
+class OffloadLayerWrapper(nn.Module):
+    """Base class: owns one unit's flat fp32 master weights, its permanent bf16 weights and the
+    scheduling of its optimizer step."""
+
+    def __init__(self, layer: nn.Module, device: torch.device, layer_idx: int,
+                 offload_device: torch.device = torch.device("cpu"), grad_pool: Optional[GradUnitPool] = None,
+                 opt_stream: Optional[torch.cuda.Stream] = None, skip_params: Optional[set] = None,
+                 tied_param: Optional[nn.Parameter] = None, enable_timing: bool = False, is_last_layer: bool = False,
+                 layer_optimizer=None, dtype: torch.dtype = torch.bfloat16, state_device: str = "hbm",
+                 shared_dp=None, update_chunk: int = UPDATE_CHUNK_SIZE):
+        super().__init__()
+        if layer_optimizer is None:
+            raise RuntimeError("a shared LayerAdam must be provided")
+        if state_device not in ("hbm", "host"):
+            raise ValueError("state_device must be 'hbm' or 'host'")
+        self.device, self.layer_idx, self.is_last_layer, self.dtype = device, layer_idx, is_last_layer, dtype
+        self.layer = layer
+        self.grad_pool = grad_pool
+        self.opt_stream = opt_stream
+        self.layer_optimizer = layer_optimizer
+        self.state_device = state_device
+        self.shared_dp = shared_dp
+        self.update_chunk = int(update_chunk)
+        self.enable_timing = enable_timing
+        self.skip_params = skip_params or set()
+        self.tied_param = tied_param
+        self._is_tied_output = tied_param is not None and tied_param in self.skip_params
+
+        self.compute_ready = torch.cuda.Event()
+        self.compute_ready_bw = torch.cuda.Event()
+        self.update_done = torch.cuda.Event()
+        self._update_recorded = False
+        self._unit = None
+        self._pending = 0          # parameters whose gradient has not been accumulated yet
+        self.timings: Dict[str, List] = {"parameter_update": []}
+
+        self._managed_named_params = [(n, p) for n, p in self.layer.named_parameters() if p not in self.skip_params]
+        self.total_size = sum(p.numel() for _, p in self._managed_named_params)
+        n = self.total_size
+
+        # ---- storage: fp32 masters (+ moments in the optimizer) and permanent bf16 weights ----
+        if shared_dp is not None:
+            st = shared_dp.register_layer(layer_idx, n)
+            self._dp_state = st
+            self._params_flat = st.params                      # this rank's fp32 slice
+            self._bf16_flat = st.bf16[:n]                      # full layer, all-gather target
+            self._dp_group = None
+        else:
+            self._dp_state = None
+            if state_device == "hbm":
+                self._params_flat = torch.empty(n, dtype=torch.float32, device=device)
+            else:
+                self._params_flat = torch.empty(n, dtype=torch.float32).pin_memory()
+            self._bf16_flat = torch.empty(n, dtype=dtype, device=device)
+
+        self._param_maps = OrderedDict()
+        self._master_views = []
+        self._bf16_views = []
+        with torch.no_grad():
+            off = 0
+            full_fp32 = torch.empty(n, dtype=torch.float32, device=device) if shared_dp is not None else None
+            for name, p in self._managed_named_params:
+                k = p.numel()
+                self._param_maps[name] = (off, p.shape, k)
+                src = p.data.detach().to(device=device, dtype=torch.float32).reshape(-1)
+                if shared_dp is not None:
+                    full_fp32[off:off + k].copy_(src)
+                else:
+                    self._params_flat[off:off + k].copy_(src, non_blocking=True)
+                self._bf16_flat[off:off + k].copy_(src)
+                p.data = self._bf16_flat[off:off + k].view(p.shape)   # the weights the layer computes with
+                p.grad = None
+                off += k
+            if shared_dp is not None:
+                shared_dp.load_full_params(layer_idx, full_fp32)
+                del full_fp32
+            else:
+                off = 0
+                for name, p in self._managed_named_params:
+                    k = p.numel()
+                    self._master_views.append(nn.Parameter(self._params_flat[off:off + k].view(p.shape), requires_grad=False))
+                    self._bf16_views.append(self._bf16_flat[off:off + k].view(p.shape))
+                    off += k
+                self.layer_optimizer.add_layer_params(layer_idx, self._master_views, self._bf16_views)
+        for module in layer.modules():   # constants stay on the compute device (transformer_layer.py:148-152)
+            for bname, buf in module.named_buffers(recurse=False):
+                if buf is not None and buf.device != device:
+                    module._buffers[bname] = buf.to(device)
+        for _, p in self._managed_named_params:
+            if p.requires_grad:
+                p.register_post_accumulate_grad_hook(self._on_param_grad)
+
+    # ---- window management (names of transformer_layer.py:273-343) ------------------------------
+    def to_device_async(self, is_bwd: bool = False):
+        """Forward needs nothing (the bf16 weights are resident).  For backward: take the next
+        gradient unit, wait until the optimizer has released it, zero it and point every
+        parameter's .grad into it, so autograd accumulates straight into the flat buffer."""
+        if not is_bwd or self._unit is not None:
+            return
+        unit = self.grad_pool.get()
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_event(unit["reuse_ready"])
+        g = unit["grad"]
+        g[: self.total_size].zero_()
+        self._pending = 0
+        for name, p in self._managed_named_params:
+            off, shape, k = self._param_maps[name]
+            if p.requires_grad:
+                p.grad = g[off:off + k].view(shape)
+                self._pending += 1
+        self._unit = unit
+
+    def wait_for_h2d(self):
+        return None
+
+    def to_offload_async(self, is_bwd: bool = False, prev_update=None):
+        """Backward: mark the gradients complete on the compute stream (the counterpart of the
+        reference handing the unit to its D2H worker)."""
+        if is_bwd:
+            self.compute_ready_bw.record(torch.cuda.current_stream(self.device))
+
+    def wait_for_d2h(self):
+        return None
+
+    def _on_param_grad(self, _param):
+        if self._unit is None:
+            return
+        self._pending -= 1
+        if self._pending == 0:
+            self.to_offload_async(is_bwd=True)
+            self.update_params()
+
+    def flush(self):
+        """Run the update for a unit whose backward finished without touching every parameter."""
+        if self._unit is not None:
+            self.to_offload_async(is_bwd=True)
+            self.update_params()
+
+    # ---- the optimizer step ----------------------------------------------------------------------
+    def update_params(self):
+        """Enqueue this unit's Adam step on the optimizer stream, behind `compute_ready_bw`."""
+        unit, self._unit = self._unit, None
+        if unit is None:
+            return None
+        n = self.total_size
+        g = unit["grad"]
+        opt = self.layer_optimizer
+        s = self.opt_stream
+        t0 = t1 = None
+        with torch.cuda.stream(s):
+            s.wait_event(self.compute_ready_bw)
+            if self.enable_timing:
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(s)
+            if self.shared_dp is not None:
+                if self._dp_group is None:
+                    self._dp_group = dict(opt.defaults, step=0)
+                self._dp_group["step"] += 1
+                self._dp_group["lr"] = opt.defaults["lr"]
+                self._dp_state.step = self._dp_group["step"]
+                for cs in range(0, n, self.update_chunk):
+                    ce = min(cs + self.update_chunk, n)
+                    self.shared_dp.fused_update(self.layer_idx, opt, self._dp_group, cs, ce, slot=unit["slot"],
+                                                gather=False)
+                self.shared_dp.all_gather_params(self.layer_idx)
+            else:
+                group = opt.begin_chunk_step(self.layer_idx)
+                m, v = opt.exp_avg_flat[self.layer_idx], opt.exp_avg_sq_flat[self.layer_idx]
+                if self.state_device == "hbm":
+                    for cs in range(0, n, self.update_chunk):
+                        ce = min(cs + self.update_chunk, n)
+                        opt.step_chunk(self._params_flat[cs:ce], g[cs:ce], m[cs:ce], v[cs:ce], group, self._bf16_flat[cs:ce])
+                else:
+                    # host-resident state: one call, chunked and double-buffered inside the library
+                    opt.step_chunk(self._params_flat, g[:n], m, v, group, self._bf16_flat)
+                opt.end_chunk_step(self.layer_idx)
+            if self.enable_timing:
+                t1.record(s)
+                self.timings["parameter_update"].append((t0, t1))
+            self.update_done.record(s)
+            unit["reuse_ready"].record(s)
+        self._update_recorded = True
+        for _, p in self._managed_named_params:
+            p.grad = None
+        return self.update_done
+
+    def wait_for_update(self):
+        """Order the compute stream after this unit's last optimizer step."""
+        if self._update_recorded:
+            torch.cuda.current_stream(self.device).wait_event(self.update_done)
+
+    def master_params_full(self) -> torch.Tensor:
+        """Flat fp32 master weights on the device (for saving); sharded state is gathered from bf16."""
+        if self.shared_dp is not None:
+            return self._bf16_flat.float()
+        return self._params_flat.to(self.device)
+
+    def forward(self, *args, **kwargs):
+        raise NotImplementedError
+
+
+class DecoderWrapper(OffloadLayerWrapper):
+    """One decoder layer under torch's non-reentrant checkpoint (transformer_layer.py:510-566)."""
+
+    def __init__(self, *args, activation_checkpoint: bool = True, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.activation_checkpoint = activation_checkpoint
+        self.activation_store = None   # set by the engine when activations go to pinned host memory
+
+    def forward(self, hidden_states, **layer_kwargs):
+        def _forward(h):
+            return call_decoder_layer(self.layer, h, layer_kwargs)
+
+        if not self.activation_checkpoint or not torch.is_grad_enabled():
+            out = _forward(hidden_states)
+        else:
+            with SlidingCheckpoint(self.layer_idx, self.activation_store, self.is_last_layer):
+                out = checkpoint(_forward, hidden_states, use_reentrant=False)
+        self.compute_ready.record(torch.cuda.current_stream(self.device))
+        return out
+
+
+class EmbeddingWrapper(OffloadLayerWrapper):
+    def forward(self, input_ids, **kwargs):
+        out = self.layer(input_ids, **kwargs)
+        self.compute_ready.record(torch.cuda.current_stream(self.device))
+        return out
+
+
+class OutputWrapper(OffloadLayerWrapper):
+    """Final norm + LM head + shifted cross entropy (transformer_layer.py:584-630).  The loss is
+    plain torch (`F.linear` + `F.cross_entropy` in fp32 over token chunks); the reference's
+    Triton fused loss is not used."""
+
+    def __init__(self, norm_layer: nn.Module, lm_head: nn.Module, *args, softcap=None, loss_chunk_tokens: int = 4096,
+                 **kwargs):
+        combined = nn.Sequential(norm_layer, lm_head)
+        super().__init__(combined, *args, **kwargs)
+        self.norm_layer, self.lm_head, self.softcap = norm_layer, lm_head, softcap
+        self.loss_chunk_tokens = int(loss_chunk_tokens)
+
+    def _logits(self, h):
+        out = F.linear(h, self.lm_head.weight, self.lm_head.bias)
+        if self.softcap is not None:
+            out = torch.tanh(out / self.softcap) * self.softcap
+        return out
+
+    def forward(self, hidden_states, labels=None):
+        h = self.norm_layer(hidden_states)
+        if labels is None:
+            out = self._logits(h)
+        else:
+            h = h[..., :-1, :].contiguous().view(-1, h.size(-1))
+            y = labels[..., 1:].contiguous().view(-1)
+            valid = (y != -100).sum().clamp(min=1)
+
+            def chunk_loss(hc, yc):
+                return F.cross_entropy(self._logits(hc).float(), yc, ignore_index=-100, reduction="sum")
+
+            total = None
+            for cs in range(0, h.shape[0], self.loss_chunk_tokens):
+                hc, yc = h[cs:cs + self.loss_chunk_tokens], y[cs:cs + self.loss_chunk_tokens]
+                part = checkpoint(chunk_loss, hc, yc, use_reentrant=False) if torch.is_grad_enabled() else chunk_loss(hc, yc)
+                total = part if total is None else total + part
+            out = total / valid
+        self.compute_ready.record(torch.cuda.current_stream(self.device))
+        return out
+
+
+def split_transformer_model(parts: TextModelParts, device: torch.device, dtype: torch.dtype = torch.bfloat16,
+                            **kwargs) -> Dict[str, Any]:
+    """Wrap embedding (idx 0), decoder layers (1..L) and norm + head (L+1) as streamed units
+    (transformer_layer.py:29-111).  A tied head weight is owned by the embedding unit and skipped
+    by the output unit; autograd sums both uses before the owner's gradient hook fires."""
+    activation_checkpoint = kwargs.pop("activation_checkpoint", True)
+    loss_chunk_tokens = kwargs.pop("loss_chunk_tokens", 4096)
+    tied = parts.tied_param
+    units = nn.ModuleList([])
+    units.append(EmbeddingWrapper(parts.embed, device, 0, dtype=dtype, tied_param=tied, **kwargs))
+    L = len(parts.layers)
+    for idx, layer in enumerate(parts.layers, start=1):
+        units.append(DecoderWrapper(layer, device, idx, dtype=dtype, is_last_layer=(idx == L),
+                                    activation_checkpoint=activation_checkpoint, **kwargs))
+    units.append(OutputWrapper(parts.norm, parts.lm_head, device, L + 1, dtype=dtype,
+                               softcap=getattr(parts.config, "final_logit_softcapping", None),
+                               skip_params={tied} if tied is not None else None, tied_param=tied,
+                               loss_chunk_tokens=loss_chunk_tokens, **kwargs))
+    return {"transformer_layers": units, "rotary_emb": parts.rotary_emb}

@@ -1,0 +1,177 @@
+"""The layer-sliding engine around the GPU optimizer (SlideFormerOffloader).
+
+What is checked
+  * the loss equals a plain forward of the same Hugging Face model (same bf16 weights);
+  * the gradients the engine hands to the optimizer match plain autograd gradients;
+  * after each step every unit's fp32 weights, moments and bf16 weights equal the CPU oracle
+    applied to exactly those gradients, bit for bit (one reference call per 32 Mi-element chunk);
+  * host-resident state, host activation offload and no-checkpoint modes give the same bits as
+    the default mode; tied embeddings (GPT-2) train the shared weight once.
+"""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+HP = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+
+
+def _bits(t):
+    return t.detach().float().cpu().numpy().view(np.uint32) if t.dtype == torch.float32 else \
+        t.detach().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _make(name, **kw):
+    from slideformer_b200.model_compat import build_random_model
+    from slideformer_b200.offload_transformer import SlideFormerOffloader
+    model = build_random_model(name, DEV, torch.bfloat16, seed=3)
+    plain = copy.deepcopy(model)
+    eng = SlideFormerOffloader(model, DEV, torch.bfloat16, enable_timing=False, enable_memory_stats=False,
+                               optimizer_kwargs=dict(HP), auto_backward_in_forward=False, **kw)
+    return eng, plain
+
+
+def _capture_grads(eng):
+    """Copy each unit's flat gradient right before its optimizer step."""
+    grabbed = {}
+    for u in eng.transformer_layers:
+        orig = u.update_params
+
+        def wrapped(u=u, orig=orig):
+            if u._unit is not None:
+                grabbed[u.layer_idx] = u._unit["grad"][: u.total_size].clone()
+            return orig()
+        u.update_params = wrapped
+    return grabbed
+
+
+def _run_steps(eng, ids_list, oracle, check_plain=None):
+    from oracle import oracle as O  # noqa: F401
+    n_units = len(eng.transformer_layers)
+    cpu = {}
+    for u in eng.transformer_layers:
+        n = u.total_size
+        cpu[u.layer_idx] = [u._params_flat.detach().cpu().numpy().copy(), np.zeros(n, np.float32), np.zeros(n, np.float32),
+                            np.zeros(n, np.uint16)]
+    orc = oracle.OracleAdam(HP["lr"], HP["betas"][0], HP["betas"][1], HP["eps"], HP["weight_decay"], True)
+    grabbed = _capture_grads(eng)
+    losses = []
+    for step, ids in enumerate(ids_list, start=1):
+        grabbed.clear()
+        if check_plain is not None and step == 1:
+            plain_out = check_plain(input_ids=ids, labels=ids)
+            plain_out.loss.backward()
+        out = eng(ids, labels=ids)
+        out.loss.backward()
+        eng.wait_for_completion()
+        losses.append(float(out.loss.detach()))
+        if check_plain is not None and step == 1:
+            assert abs(float(plain_out.loss) - losses[0]) < 2e-2 * abs(float(plain_out.loss)), (float(plain_out.loss), losses[0])
+        assert sorted(grabbed) == list(range(n_units)), f"units updated: {sorted(grabbed)}"
+        # the optimizer stream consumes units in backward order: output unit first, embedding last
+        for idx in range(n_units - 1, -1, -1):
+            u = eng.transformer_layers[idx]
+            g = grabbed[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+            p, m, v, o = cpu[idx]
+            for cs in range(0, u.total_size, u.update_chunk):
+                ce = min(cs + u.update_chunk, u.total_size)
+                orc.adam_update(step, HP["lr"], *HP["betas"], HP["eps"], HP["weight_decay"], True,
+                                p[cs:ce], g[cs:ce], m[cs:ce], v[cs:ce], o[cs:ce])
+    for idx in range(n_units):
+        u = eng.transformer_layers[idx]
+        p, m, v, o = cpu[idx]
+        assert np.array_equal(_bits(u._params_flat.to(DEV)), p.view(np.uint32)), f"unit {idx} p"
+        assert np.array_equal(_bits(eng.layer_optimizer.exp_avg_flat[idx].to(DEV)), m.view(np.uint32)), f"unit {idx} m"
+        assert np.array_equal(_bits(eng.layer_optimizer.exp_avg_sq_flat[idx].to(DEV)), v.view(np.uint32)), f"unit {idx} v"
+        assert np.array_equal(_bits(u._bf16_flat), o), f"unit {idx} bf16"
+        # the module's live parameters ARE the bf16 weights
+        name, prm = u._managed_named_params[0]
+        off, shape, k = u._param_maps[name]
+        assert prm.data.data_ptr() == u._bf16_flat[off:off + k].data_ptr()
+    return losses, grabbed
+
+
+def _ids(vocab, batch, seq, n, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (batch, seq), generator=gen).to(DEV) for _ in range(n)]
+
+
+@pytest.mark.parametrize("name", ["llama-tiny", "gpt2-tiny"])
+def test_engine_steps_match_oracle_and_plain_model(name, oracle):
+    eng, plain = _make(name)
+    vocab = eng.config.vocab_size
+    ids = _ids(vocab, 2, 32, 3)
+    losses, grabbed = _run_steps(eng, ids, oracle, check_plain=plain)
+    assert all(np.isfinite(losses))
+    assert losses[-1] < losses[0] + 0.5
+    # gradients of the last step vs plain autograd on a model holding the engine's weights of that step
+    # (step 1 comparison): rerun step-1 gradients on the plain copy
+    eng2, plain2 = _make(name)
+    g2 = _capture_grads(eng2)
+    out = eng2(ids[0], labels=ids[0])
+    out.loss.backward()
+    eng2.wait_for_completion()
+    plain2.zero_grad()
+    plain2(input_ids=ids[0], labels=ids[0]).loss.backward()
+    named = dict(plain2.named_parameters())
+    for u in eng2.transformer_layers[1:-1]:
+        flat = g2[u.layer_idx].float()
+        prefix = ("model.layers." if name.startswith("llama") else "transformer.h.") + f"{u.layer_idx - 1}."
+        for pname, (off, shape, k) in u._param_maps.items():
+            ref = named[prefix + pname].grad.float().reshape(-1)
+            got = flat[off:off + k]
+            denom = ref.norm().item() + 1e-12
+            assert (got - ref).norm().item() / denom < 5e-2, (u.layer_idx, pname)
+
+
+def test_tied_embedding_is_owned_once():
+    eng, _ = _make("gpt2-tiny")
+    assert eng.is_tied
+    wte = eng.parts.embed.wte.weight
+    assert eng.parts.lm_head.weight is wte
+    assert any(p is wte for _, p in eng.embed_layer._managed_named_params)
+    assert not any(p is wte for _, p in eng.output_layer._managed_named_params)
+    total = sum(u.total_size for u in eng.transformer_layers)
+    assert total == sum(p.numel() for p in eng.base_model.parameters())
+
+
+@pytest.mark.parametrize("kw", [dict(state_device="host"), dict(activation_offload="host"),
+                                dict(activation_checkpoint=False), dict(double_buffer=True),
+                                dict(update_chunk=4096)])
+def test_engine_modes_agree_bitwise(kw, oracle):
+    base, _ = _make("llama-tiny")
+    other, _ = _make("llama-tiny", **kw)
+    # a different chunking is a different reference call sequence (pow() vs running product for
+    # beta^t), so it is compared after one step, before the weights can drift apart
+    ids = _ids(base.config.vocab_size, 2, 32, 1 if "update_chunk" in kw else 3, seed=9)
+    for e in (base, other):
+        for x in ids:
+            e(x, labels=x).loss.backward()
+            e.wait_for_completion()
+    for ub, uo in zip(base.transformer_layers, other.transformer_layers):
+        if "update_chunk" in kw:
+            # within north_star's 2-ulp budget
+            a, b = ub._params_flat.cpu().numpy(), uo._params_flat.cpu().numpy()
+            assert np.max(np.abs(a.view(np.int32).astype(np.int64) - b.view(np.int32).astype(np.int64))) <= 2
+        else:
+            assert np.array_equal(_bits(ub._params_flat.to(DEV)), _bits(uo._params_flat.to(DEV))), ub.layer_idx
+            assert np.array_equal(_bits(ub._bf16_flat), _bits(uo._bf16_flat))
+    if kw.get("activation_offload") == "host":
+        st = other.activation_store
+        assert st is not None and st.bytes_d2h > 0 and st.bytes_h2d > 0
+
+
+def test_inference_forward_and_lr_update():
+    eng, plain = _make("llama-tiny")
+    ids = _ids(eng.config.vocab_size, 2, 16, 1)[0]
+    with torch.no_grad():
+        logits = eng(ids).logits
+        ref = plain(input_ids=ids).logits
+    assert logits.shape == ref.shape
+    assert (logits.float() - ref.float()).abs().max().item() < 0.1
+    eng.update_learning_rate(5e-4)
+    assert eng.layer_optimizer.defaults["lr"] == 5e-4
+    assert all(g["lr"] == 5e-4 for g in eng.layer_optimizer.param_groups)
