@@ -378,6 +378,31 @@ def main_b200(args):
         cpu_baseline = {"value": r["value"], "unit": "Gparams/s", "cores": r["cores"], "kind": r["kind"],
                         "sample": r["sample"], "ms_per_step": r["ms_per_step"], "bf16_cast_ms": r["bf16_cast_ms"]}
 
+    # ---- fine-tune tokens/s with the same kernel inside the layer-sliding engine ------------------
+    finetune = None
+    if args.finetune != "none":
+        import gc
+        from slideformer_b200.finetune_bench import run_finetune
+        if world == 1:
+            del p, m, v, out, grads, g_host, out_host, stepper, opt
+        else:
+            sh.close()
+            del sh
+        gc.collect()
+        torch.cuda.empty_cache()
+        jobs = [("gpt2-small", 10, 3, "hbm"), ("llama3.1-8b", 4, 2, "hbm")]
+        if args.finetune == "full" and world == 1:
+            jobs.append(("llama3.1-8b", 3, 1, "host"))
+        finetune = []
+        for name, fsteps, fwarm, state_dev in jobs:
+            dp = None
+            if world > 1:
+                from slideformer_b200.shared_data_parallel import SharedDataParallel
+                dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=2)
+            finetune.append(run_finetune(name, 8, 1024, fsteps, fwarm, dev, world, rank, dp, state_device=state_dev))
+            if dp is not None:
+                dp.close()
+
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "Gparams/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
@@ -388,6 +413,8 @@ def main_b200(args):
                 "hbm_gbs": BYTES_PER_PARAM * value, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
                 "gpu_launches": int(launches), "clocks": sampler.summary()}
         line.update(extra)
+        if finetune is not None:
+            line["finetune"] = finetune
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -406,6 +433,9 @@ def main():
     ap.add_argument("--host-state", action="store_true", default=True)
     ap.add_argument("--no-host-state", dest="host_state", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--finetune", default="all", choices=["none", "all", "full"],
+                    help="also report fine-tune tokens/s of GPT-2 small and Llama-3.1-8B through the engine "
+                         "(batch 8 x 1024 per GPU); 'full' adds the host-pinned-state mode at N=1")
     args = ap.parse_args()
     if args.impl == "reference":
         return main_reference(args)

@@ -34,6 +34,85 @@ def model_flops_per_step(cfg, batch, seq):
     return 12 * batch * seq * L * h * h * ((1 + kv / heads + seq / h) + (inter / h) * gated + V / (2 * L * h))
 
 
+def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int, dev, world: int = 1, rank: int = 0,
+                 dp=None, layers=None, state_device: str = "hbm", activation_offload: str = "hbm",
+                 activation_checkpoint: bool = True, double_buffer: bool = False, lr: float = 1e-5) -> dict:
+    """Build the random-init model, run warm-up + timed steps, return the result line as a dict.
+    `dp` is a SharedDataParallel (state sharded over the ranks of the default process group) or None."""
+    from slideformer_b200 import _lib
+    from slideformer_b200.model_compat import build_random_model
+    from slideformer_b200.offload_transformer import SlideFormerOffloader
+
+    lib = _lib.load()
+    torch.cuda.reset_peak_memory_stats(dev)
+    t_build = time.perf_counter()
+    model = build_random_model(model_name, dev, torch.bfloat16, seed=0, num_layers=layers)
+    engine = SlideFormerOffloader(
+        model, dev, torch.bfloat16, double_buffer=double_buffer, enable_timing=True, enable_memory_stats=False,
+        optimizer_kwargs=dict(lr=lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01),
+        shared_dp=dp, state_device=state_device, activation_offload=activation_offload,
+        activation_checkpoint=activation_checkpoint)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t_build
+
+    vocab = model.config.vocab_size
+    gen = torch.Generator().manual_seed(1234 + rank)
+    nb = 4
+    host_ids = [torch.randint(0, vocab, (batch, seq), generator=gen).pin_memory() for _ in range(nb)]
+    loss_host = torch.zeros(1).pin_memory()
+
+    def step(i):
+        ids = host_ids[i % nb].to(dev, non_blocking=True)
+        out = engine(ids, labels=ids)
+        loss_host.copy_(out.loss.detach().float().reshape(1), non_blocking=True)
+        return out
+
+    losses = []
+    for i in range(warmup):
+        step(i)
+        torch.cuda.synchronize()
+        losses.append(float(loss_host.item()))
+    if dp is not None:
+        dp.barrier()
+    torch.cuda.synchronize()
+    l0 = lib.sf_launch_count()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    a.record()
+    for i in range(steps):
+        step(i)
+    b.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    losses.append(float(loss_host.item()))
+    ms = max(a.elapsed_time(b), wall * 1e3) / steps
+    if dp is not None:
+        t = torch.tensor([ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    tokens = batch * seq * world
+    upd = engine.parameter_update_ms()
+    flops = model_flops_per_step(model.config, batch, seq) * world
+    line = {"metric": "fine-tune tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{model_name} full fine-tune, layer sliding", "global_batch": batch * world,
+                       "seq_len": seq, "state_device": state_device, "activation_offload": activation_offload,
+                       "activation_checkpoint": activation_checkpoint,
+                       "parallelism": f"dp{world} sharded state" if dp is not None else "single GPU"},
+            "model_tflops": flops / (ms * 1e-3) / 1e12, "params": sum(u.total_size for u in engine.transformer_layers),
+            "optimizer_ms_per_step": sum(upd.values()), "optimizer_ms_decoder_layer": upd.get(1),
+            "gpu_launches": int(lib.sf_launch_count() - l0), "loss_first": losses[0] if losses else None,
+            "loss_last": losses[-1], "build_seconds": build_s,
+            "max_memory_gb": torch.cuda.max_memory_allocated(dev) / 2**30,
+            "e2e": {"h2d_bytes_per_step": batch * seq * 8 * world, "d2h_bytes_per_step": 4 * world}}
+    del engine, model
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return line
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="gpt2-small")
@@ -50,10 +129,6 @@ def main(argv=None):
     ap.add_argument("--lr", type=float, default=1e-5)
     args = ap.parse_args(argv)
 
-    from slideformer_b200 import _lib
-    from slideformer_b200.model_compat import build_random_model
-    from slideformer_b200.offload_transformer import SlideFormerOffloader
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -65,69 +140,8 @@ def main(argv=None):
         from slideformer_b200.shared_data_parallel import SharedDataParallel
         dist.init_process_group("nccl", device_id=dev)
         dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=3 if args.double_buffer else 2)
-    lib = _lib.load()
-
-    t_build = time.perf_counter()
-    model = build_random_model(args.model, dev, torch.bfloat16, seed=0, num_layers=args.layers)
-    engine = SlideFormerOffloader(
-        model, dev, torch.bfloat16, double_buffer=args.double_buffer, enable_timing=True, enable_memory_stats=False,
-        optimizer_kwargs=dict(lr=args.lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01),
-        shared_dp=dp, state_device=args.state_device, activation_offload=args.activation_offload,
-        activation_checkpoint=not args.no_ckpt)
-    torch.cuda.synchronize()
-    build_s = time.perf_counter() - t_build
-
-    vocab = model.config.vocab_size
-    gen = torch.Generator().manual_seed(1234 + rank)
-    nb = 4
-    host_ids = [torch.randint(0, vocab, (args.batch, args.seq), generator=gen).pin_memory() for _ in range(nb)]
-    loss_host = torch.zeros(1).pin_memory()
-
-    def step(i):
-        ids = host_ids[i % nb].to(dev, non_blocking=True)
-        out = engine(ids, labels=ids)
-        loss_host.copy_(out.loss.detach().float().reshape(1), non_blocking=True)
-        return out
-
-    losses = []
-    for i in range(args.warmup):
-        step(i)
-        torch.cuda.synchronize()
-        losses.append(float(loss_host.item()))
-    if dp is not None:
-        dp.barrier()
-    torch.cuda.synchronize()
-    l0 = lib.sf_launch_count()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
-    a.record()
-    for i in range(args.steps):
-        step(i)
-    b.record()
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    losses.append(float(loss_host.item()))
-    ms = max(a.elapsed_time(b), wall * 1e3) / args.steps
-    if dp is not None:
-        t = torch.tensor([ms], device=dev)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms = float(t.item())
-    tokens = args.batch * args.seq * world
-    upd = engine.parameter_update_ms()
-    flops = model_flops_per_step(model.config, args.batch, args.seq) * world
-    line = {"metric": "fine-tune tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.model} full fine-tune, layer sliding", "global_batch": args.batch * world,
-                       "seq_len": args.seq, "state_device": args.state_device,
-                       "activation_offload": args.activation_offload, "activation_checkpoint": not args.no_ckpt,
-                       "parallelism": f"dp{world} sharded state" if dp is not None else "single GPU"},
-            "model_tflops": flops / (ms * 1e-3) / 1e12, "params": sum(u.total_size for u in engine.transformer_layers),
-            "optimizer_ms_per_step": sum(upd.values()), "optimizer_ms_decoder_layer": upd.get(1),
-            "gpu_launches": int(lib.sf_launch_count() - l0), "loss_first": losses[0] if losses else None,
-            "loss_last": losses[-1], "build_seconds": build_s,
-            "max_memory_gb": torch.cuda.max_memory_allocated() / 2**30,
-            "e2e": {"h2d_bytes_per_step": args.batch * args.seq * 8 * world, "d2h_bytes_per_step": 4 * world}}
+    line = run_finetune(args.model, args.batch, args.seq, args.steps, args.warmup, dev, world, rank, dp, args.layers,
+                        args.state_device, args.activation_offload, not args.no_ckpt, args.double_buffer, args.lr)
     if rank == 0:
         print(json.dumps(line))
     if dp is not None:
