@@ -45,6 +45,19 @@ def ncu_traffic_bytes(units: int) -> float:
     return 14.0 * units + max(14.0 * units - 56e6, 0.0)
 
 
+_RESULT_FD = None
+
+
+def emit(line: str) -> None:
+    """Write the result line to the real stdout (see main)."""
+    data = (line + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(line + "\n")
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def measured_peak():
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
@@ -212,8 +225,38 @@ def main_reference(args):
                              "sample": r["sample"]},
             "e2e": {"value": r["value"], "unit": "Gparams/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    emit(json.dumps(line))
     return 0
+
+
+def measure_pcie(dev, nbytes: int = 1 << 30, reps: int = 5) -> dict:
+    """Plain pinned-memory copy bandwidth of this box: each direction alone and both at once.
+    The denominators for the host-buffer paths (PCIe Gen5 x16: 63 GB/s per direction nominal)."""
+    import torch
+    h_in = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    d_out = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def timed(up: bool, down: bool) -> float:
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            if up:
+                with torch.cuda.stream(s1):
+                    d_in.copy_(h_in, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s2):
+                    h_out.copy_(d_out, non_blocking=True)
+        torch.cuda.synchronize(dev)
+        return (time.perf_counter() - t0) / reps
+
+    timed(True, True)
+    up, down, both = timed(True, False), timed(False, True), timed(True, True)
+    return {"h2d_gbs": nbytes / up / 1e9, "d2h_gbs": nbytes / down / 1e9,
+            "bidirectional_each_gbs": nbytes / both / 1e9, "nominal_gen5_x16_gbs": 63.0,
+            "how": f"{nbytes >> 20} MiB pinned copies, {reps} repetitions, wall clock around a device synchronize"}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -273,7 +316,7 @@ def main_b200(args):
 
         def one_step(i):
             sh.step(i % NG)
-        hbm_bytes_per_launch = BYTES_PER_PARAM * sh.shard_numel + 2 * sh.shard_numel * (world - 1 if args.dp_mode == "fused" else 0)
+        hbm_bytes_per_launch = BYTES_PER_PARAM * sh.shard_numel + 2 * sh.shard_numel * (world - 1 if args.dp_mode != "nccl" else 0)
         parallelism = f"dp{world}: state sharded 1/{world}, {sh.describe()}"
         scaling = "strong"
 
@@ -347,6 +390,7 @@ def main_b200(args):
                "d2h_bytes_per_step": 2 * n, "ms_per_step": e2e_ms, "steps": E,
                "path": "HostGradStepper: pinned bf16 gradient -> HBM-resident LayerAdam.step_chunk -> pinned bf16 weights, "
                        f"{args.e2e_chunk}-element chunks on three streams"}
+        extra["pcie"] = measure_pcie(dev)
         # fully host-resident state (p, m, v and g in pinned host memory) streamed through the GPU
         if args.host_state:
             ph, mh, vh = (torch.empty(n).pin_memory() for _ in range(3))
@@ -415,20 +459,26 @@ def main_b200(args):
         line.update(extra)
         if finetune is not None:
             line["finetune"] = finetune
-        print(json.dumps(line))
+        emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
     return 0
 
 
 def main():
+    # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line
+    # there, so everything but the final line is sent to stderr at the file-descriptor level.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--n", type=int, default=N_LAYER, help="flat layer size (parity and sweep runs only)")
-    ap.add_argument("--dp-mode", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--dp-mode", default="fused", choices=["fused", "fused_ag", "nccl"])
     ap.add_argument("--e2e-chunk", type=int, default=16 * 1024 * 1024)
     ap.add_argument("--host-state", action="store_true", default=True)
     ap.add_argument("--no-host-state", dest="host_state", action="store_false")

@@ -118,6 +118,18 @@ int sf_adam_step_sharded(const SfAdamScalars* s, float* p, const void* const* pe
                          int g_dtype, float* m, float* v, uint16_t* p_bf16, uint64_t n,
                          uint64_t vec_n, void* stream);
 
+/* sf_adam_step_sharded with the parameter all-gather folded in as well: the bf16 copy of the
+ * updated slice is stored into EVERY rank's bf16 layer buffer (peer_out[r] = device pointer,
+ * local or peer-mapped, to rank r's buffer at this slice; world entries) from the same kernel
+ * that pulls the gradients, so the pushes (NVLink egress) overlap the pulls (ingress) and the
+ * reference's "publish the weights to all ranks" step (one shared fp32 mapping read by every
+ * rank, multi_gpu/shared_data_parallel.py:92-105) needs no separate collective.  The caller
+ * orders the launch after all ranks wrote their gradients and must place a cross-rank stream
+ * barrier after it before any rank reads the bf16 buffers.  The kernel never waits on a peer. */
+int sf_adam_step_sharded_push(const SfAdamScalars* s, float* p, const void* const* peer_g,
+                               uint16_t* const* peer_out, int world, int g_dtype, float* m, float* v,
+                               uint64_t n, uint64_t vec_n, void* stream);
+
 /* The gradient mean alone, for callers that keep the reference's update(params, mean, m, v)
  * callback (shared_data_parallel.py:130-135): mean[i] = (0 + g_0[i] + ... + g_{world-1}[i]) / world
  * in fp32, rank order.  mean is a local fp32[n] device buffer. */

@@ -36,7 +36,8 @@ def model_flops_per_step(cfg, batch, seq):
 
 def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int, dev, world: int = 1, rank: int = 0,
                  dp=None, layers=None, state_device: str = "hbm", activation_offload: str = "hbm",
-                 activation_checkpoint: bool = True, double_buffer: bool = False, lr: float = 1e-5) -> dict:
+                 activation_checkpoint: bool = True, double_buffer: bool = False, lr: float = 1e-5,
+                 weight_window: bool = False, meta: bool = False) -> dict:
     """Build the random-init model, run warm-up + timed steps, return the result line as a dict.
     `dp` is a SharedDataParallel (state sharded over the ranks of the default process group) or None."""
     from slideformer_b200 import _lib
@@ -46,12 +47,12 @@ def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int,
     lib = _lib.load()
     torch.cuda.reset_peak_memory_stats(dev)
     t_build = time.perf_counter()
-    model = build_random_model(model_name, dev, torch.bfloat16, seed=0, num_layers=layers)
+    model = build_random_model(model_name, dev, torch.bfloat16, seed=0, num_layers=layers, meta=meta)
     engine = SlideFormerOffloader(
         model, dev, torch.bfloat16, double_buffer=double_buffer, enable_timing=True, enable_memory_stats=False,
         optimizer_kwargs=dict(lr=lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01),
         shared_dp=dp, state_device=state_device, activation_offload=activation_offload,
-        activation_checkpoint=activation_checkpoint)
+        activation_checkpoint=activation_checkpoint, weight_window=weight_window)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t_build
 
@@ -98,7 +99,7 @@ def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{model_name} full fine-tune, layer sliding", "global_batch": batch * world,
                        "seq_len": seq, "state_device": state_device, "activation_offload": activation_offload,
-                       "activation_checkpoint": activation_checkpoint,
+                       "activation_checkpoint": activation_checkpoint, "weight_window": weight_window,
                        "parallelism": f"dp{world} sharded state" if dp is not None else "single GPU"},
             "model_tflops": flops / (ms * 1e-3) / 1e12, "params": sum(u.total_size for u in engine.transformer_layers),
             "optimizer_ms_per_step": sum(upd.values()), "optimizer_ms_decoder_layer": upd.get(1),
@@ -127,6 +128,9 @@ def main(argv=None):
     ap.add_argument("--double-buffer", action="store_true")
     ap.add_argument("--dp", action="store_true", help="shard optimizer state over all ranks (launch with torchrun)")
     ap.add_argument("--lr", type=float, default=1e-5)
+    ap.add_argument("--weight-window", action="store_true",
+                    help="keep only bf16 slices resident and all-gather each layer into a window unit before it runs")
+    ap.add_argument("--meta", action="store_true", help="build the model skeleton on the meta device (large models)")
     args = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -141,7 +145,8 @@ def main(argv=None):
         dist.init_process_group("nccl", device_id=dev)
         dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=3 if args.double_buffer else 2)
     line = run_finetune(args.model, args.batch, args.seq, args.steps, args.warmup, dev, world, rank, dp, args.layers,
-                        args.state_device, args.activation_offload, not args.no_ckpt, args.double_buffer, args.lr)
+                        args.state_device, args.activation_offload, not args.no_ckpt, args.double_buffer, args.lr,
+                        args.weight_window, args.meta)
     if rank == 0:
         print(json.dumps(line))
     if dp is not None:

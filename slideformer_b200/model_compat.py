@@ -126,8 +126,10 @@ MODEL_SPECS = {
 
 
 def build_random_model(name: str, device, dtype=torch.bfloat16, seed: int = 0, attn_implementation: str = "sdpa",
-                       num_layers: Optional[int] = None):
-    """Random-init model of a named architecture, created directly on `device` in `dtype`."""
+                       num_layers: Optional[int] = None, meta: bool = False):
+    """Random-init model of a named architecture, created directly on `device` in `dtype`.
+    meta=True builds only the module skeleton (parameters on the meta device); the engine then
+    creates every unit's weights in place, so a model larger than one GPU never exists whole."""
     spec = dict(MODEL_SPECS[name])
     family = spec.pop("family")
     if num_layers is not None:
@@ -136,7 +138,7 @@ def build_random_model(name: str, device, dtype=torch.bfloat16, seed: int = 0, a
     old = torch.get_default_dtype()
     torch.set_default_dtype(dtype)
     try:
-        with torch.device(device):
+        with torch.device("meta" if meta else device):
             if family == "gpt2":
                 from transformers import GPT2Config, GPT2LMHeadModel
                 cfg = GPT2Config(resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0, attn_implementation=attn_implementation,
@@ -149,4 +151,8 @@ def build_random_model(name: str, device, dtype=torch.bfloat16, seed: int = 0, a
                 model = LlamaForCausalLM(cfg)
     finally:
         torch.set_default_dtype(old)
+    if meta and family != "gpt2":
+        dec = model.get_decoder()
+        if getattr(dec, "rotary_emb", None) is not None:   # its frequency table is a buffer, not a parameter
+            dec.rotary_emb = type(dec.rotary_emb)(config=cfg, device=device)
     return model

@@ -30,7 +30,8 @@ import torch.nn as nn
 from .layer_adam import LayerAdam
 from .model_compat import parameter_sizes, prepare_layer_inputs, validate_model
 from .sliding_checkpoint import ActivationStore
-from .transformer_layer import GradUnitPool, split_transformer_model
+from .shared_data_parallel import shard_numel
+from .transformer_layer import GradUnitPool, WeightUnitPool, split_transformer_model
 
 
 class CausalLMOutput(dict):
@@ -49,7 +50,7 @@ class SlideFormerOffloader(nn.Module):
                  enable_memory_stats: bool = True, optimizer_kwargs: Optional[dict] = None,
                  auto_backward_in_forward: bool = True, shared_dp=None, *, state_device: str = "hbm",
                  activation_offload: str = "hbm", activation_checkpoint: bool = True, loss_chunk_tokens: int = 4096,
-                 update_chunk: Optional[int] = None):
+                 update_chunk: Optional[int] = None, weight_window: bool = False):
         super().__init__()
         if not isinstance(device, torch.device):
             raise TypeError("device must be torch.device")
@@ -91,7 +92,17 @@ class SlideFormerOffloader(nn.Module):
             shared_dp._grow_exchange(-(-self.max_param_size // (16 * shared_dp.world_size)) * 16 * shared_dp.world_size)
         self._grad_pool = None  # built after the layers registered (the exchange buffers may grow)
 
-        kwargs = dict(opt_stream=self.opt_stream, enable_timing=enable_timing, layer_optimizer=self.layer_optimizer,
+        self.weight_window = bool(weight_window)
+        self.weight_pool = self.comm_stream = None
+        if self.weight_window:
+            if shared_dp is None:
+                raise ValueError("weight_window needs shared_dp (sharded optimizer state)")
+            with torch.cuda.device(device):
+                self.comm_stream = torch.cuda.Stream()
+            unit_elems = shard_numel(self.max_param_size, shared_dp.world_size) * shared_dp.world_size
+            self.weight_pool = WeightUnitPool(3 if double_buffer else 2, unit_elems, dtype, device)
+        kwargs = dict(weight_pool=self.weight_pool, comm_stream=self.comm_stream,
+                      opt_stream=self.opt_stream, enable_timing=enable_timing, layer_optimizer=self.layer_optimizer,
                       state_device=state_device, shared_dp=shared_dp, activation_checkpoint=activation_checkpoint,
                       loss_chunk_tokens=loss_chunk_tokens)
         if update_chunk is not None:
@@ -116,16 +127,35 @@ class SlideFormerOffloader(nn.Module):
 
     # ---- hooks (offload_transformer.py:221-308) ---------------------------------------------------
     def _register_layer_hooks(self):
+        units = self.transformer_layers
+        last = len(units) - 1
+
         def pre_forward(module, args):
+            if self.weight_window:
+                module.to_device_async()                       # no-op if the prefetch already took a unit
+                if module.layer_idx < last:
+                    units[module.layer_idx + 1].to_device_async()   # prefetch the next unit's weights
+                module.wait_for_h2d()
             module.wait_for_update()
+            return None
+
+        def post_forward(module, args, output):
+            # the output unit keeps its weights: its backward starts right away
+            if self.weight_window and (module.layer_idx < last or not torch.is_grad_enabled()):
+                module.release_weights()
             return None
 
         def pre_backward(module, grad_output):
             module.to_device_async(is_bwd=True)
+            if self.weight_window:
+                if module.layer_idx > 1:
+                    units[module.layer_idx - 1].to_device_async()   # prefetch the previous unit's weights
+                module.wait_for_h2d()
             return None
 
-        for unit in self.transformer_layers:
+        for unit in units:
             unit.register_forward_pre_hook(pre_forward)
+            unit.register_forward_hook(post_forward)
             unit.register_full_backward_pre_hook(pre_backward)
 
     def wait_for_completion(self) -> None:

@@ -68,6 +68,9 @@ class LayerState:
     start: int = 0           # global range of the slice, clipped to numel
     end: int = 0
     bf16: Optional[torch.Tensor] = None  # full layer, bf16, padded to shard * world: all-gather target
+    peer_bf16: Optional[list] = None     # base pointer of every rank's `bf16` (push mode only)
+    bf16_shard: Optional[torch.Tensor] = None  # window mode: only this rank's bf16 slice is kept; the full
+                                               # layer is all-gathered into a window unit when it is needed
 
 
 class _RawCuda:
@@ -116,7 +119,7 @@ class SharedDataParallel:
     chunk order on every rank."""
 
     def __init__(self, chunk_numel=32 * 1024 * 1024, dtype=torch.bfloat16, shm_dir=None, timeout_seconds=120,
-                 *, device=None, exchange_slots: int = 2):
+                 *, device=None, exchange_slots: int = 2, push_weights: bool = True):
         if not dist.is_initialized():
             raise RuntimeError("Initialize torch.distributed before SharedDataParallel")
         if chunk_numel < 1:
@@ -139,9 +142,13 @@ class SharedDataParallel:
         self._lib = _lib.load()
         self._gcode = _lib.SF_GRAD_BF16 if dtype == torch.bfloat16 else _lib.SF_GRAD_F32
         self._esize = 2 if dtype == torch.bfloat16 else 4
-        if not self.ctl.all_same((socket.gethostname(), self.chunk_numel, str(dtype), exchange_slots)):
+        if not self.ctl.all_same((socket.gethostname(), self.chunk_numel, str(dtype), exchange_slots, bool(push_weights))):
             raise ValueError("SharedDataParallel requires one host and matching chunk size/dtype")
         self.exchange_slots = int(exchange_slots)
+        # True: the update kernel stores the bf16 weights into every rank's layer buffer itself
+        # (peer-mapped stores); False: NCCL all-gather after the kernel.
+        self.push_weights = bool(push_weights)
+        self._weight_allocs = []            # (base, peers) of the IPC-visible bf16 layer buffers
         self._cap = 0                       # elements per exchange slot
         self._base = None                   # local exchange allocation (raw pointer)
         self._peer_base: List[int] = []     # every rank's exchange base mapped here (own = local pointer)
@@ -150,17 +157,42 @@ class SharedDataParallel:
         self._token = torch.zeros(1, device=self.device)
         self.group = self.ctl.group
 
-    # ---- exchange buffers ------------------------------------------------------------------
-    def _free_exchange(self):
-        for r, ptr in enumerate(self._peer_base):
+    # ---- memory every rank can address (CUDA IPC) --------------------------------------------------
+    def _shared_alloc(self, nbytes: int):
+        """Collective: allocate `nbytes` on every rank, exchange IPC handles, map the peers'.
+        Returns (local base pointer, [base pointer of rank r as seen from this process])."""
+        with torch.cuda.device(self.device):
+            ptr = C.c_void_p()
+            _lib.check(self._lib.sf_dev_alloc(nbytes, C.byref(ptr)))
+            base = ptr.value
+            handle = (C.c_ubyte * _lib.SF_IPC_HANDLE_BYTES)()
+            _lib.check(self._lib.sf_ipc_export(base, handle))
+            handles = self.ctl.gather(bytes(handle))
+            peers = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    peers.append(base)
+                    continue
+                buf = (C.c_ubyte * _lib.SF_IPC_HANDLE_BYTES).from_buffer_copy(h)
+                out = C.c_void_p()
+                _lib.check(self._lib.sf_ipc_open(buf, C.byref(out)))
+                peers.append(out.value)
+        return base, peers
+
+    def _shared_free(self, base, peers):
+        for r, ptr in enumerate(peers):
             if r != self.rank and ptr:
                 self._lib.sf_ipc_close(ptr)
-        self._peer_base = []
-        self._exchange = []
-        if self._base:
+        if base:
             with torch.cuda.device(self.device):
-                _lib.check(self._lib.sf_dev_free(self._base))
-            self._base = None
+                _lib.check(self._lib.sf_dev_free(base))
+
+    # ---- exchange buffers ------------------------------------------------------------------
+    def _free_exchange(self):
+        self._exchange = []
+        self._shared_free(self._base, self._peer_base)
+        self._peer_base = []
+        self._base = None
 
     def _grow_exchange(self, elems: int):
         """Collective: (re)allocate the exchange slots for `elems` elements and map the peers'."""
@@ -171,22 +203,8 @@ class SharedDataParallel:
         self._free_exchange()
         elems = -(-elems // 128) * 128
         nbytes = elems * self._esize * self.exchange_slots
+        self._base, self._peer_base = self._shared_alloc(nbytes)
         with torch.cuda.device(self.device):
-            ptr = C.c_void_p()
-            _lib.check(self._lib.sf_dev_alloc(nbytes, C.byref(ptr)))
-            self._base = ptr.value
-            handle = (C.c_ubyte * _lib.SF_IPC_HANDLE_BYTES)()
-            _lib.check(self._lib.sf_ipc_export(self._base, handle))
-            handles = self.ctl.gather(bytes(handle))
-            self._peer_base = []
-            for r, h in enumerate(handles):
-                if r == self.rank:
-                    self._peer_base.append(self._base)
-                    continue
-                buf = (C.c_ubyte * _lib.SF_IPC_HANDLE_BYTES).from_buffer_copy(h)
-                out = C.c_void_p()
-                _lib.check(self._lib.sf_ipc_open(buf, C.byref(out)))
-                self._peer_base.append(out.value)
             flat = torch.as_tensor(_RawCuda(self._base, nbytes), device=self.device)
             flat.zero_()
             self._exchange = [flat[k * elems * self._esize:(k + 1) * elems * self._esize].view(self.dtype)
@@ -207,19 +225,32 @@ class SharedDataParallel:
         return arr
 
     # ---- registration ----------------------------------------------------------------------
-    def register_layer(self, layer_idx, numel) -> LayerState:
+    def register_layer(self, layer_idx, numel, resident_bf16: bool = True) -> LayerState:
         if not self.ctl.all_same((layer_idx, int(numel))) or layer_idx in self.layers:
             raise ValueError("Ranks must register identical layers exactly once")
         numel = int(numel)
         s = shard_numel(numel, self.world_size)
         a, b = shard_range(numel, self.world_size, self.rank)
         dev = self.device
+        peer_bf16 = None
+        bf16_shard = None
+        if not resident_bf16:
+            bf16 = None
+            bf16_shard = torch.zeros(s, dtype=torch.bfloat16, device=dev)
+        elif self.push_weights and s > 0:
+            nbytes = s * self.world_size * 2
+            base, peer_bf16 = self._shared_alloc(nbytes)
+            self._weight_allocs.append((base, peer_bf16))
+            with torch.cuda.device(dev):
+                bf16 = torch.as_tensor(_RawCuda(base, nbytes), device=dev).view(torch.bfloat16)
+                bf16.zero_()
+        else:
+            bf16 = torch.zeros(s * self.world_size, dtype=torch.bfloat16, device=dev)
         state = LayerState(
             params=torch.zeros(s, dtype=torch.float32, device=dev),
             exp_avg=torch.zeros(s, dtype=torch.float32, device=dev),
             exp_avg_sq=torch.zeros(s, dtype=torch.float32, device=dev),
-            numel=numel, shard=s, start=a, end=b,
-            bf16=torch.zeros(s * self.world_size, dtype=torch.bfloat16, device=dev))
+            numel=numel, shard=s, start=a, end=b, bf16=bf16, peer_bf16=peer_bf16, bf16_shard=bf16_shard)
         self._grow_exchange(s * self.world_size)
         self.layers[layer_idx] = state
         return state
@@ -228,7 +259,19 @@ class SharedDataParallel:
         """Initialise this rank's slice (and the bf16 copy) from a full flat fp32 layer."""
         st = self.layers[layer_idx]
         st.params[: st.end - st.start].copy_(full_fp32[st.start:st.end])
-        st.bf16[: st.numel].copy_(full_fp32[: st.numel])
+        if st.bf16 is not None:
+            st.bf16[: st.numel].copy_(full_fp32[: st.numel])
+        else:
+            st.bf16_shard[: st.end - st.start].copy_(full_fp32[st.start:st.end])
+
+    @torch.no_grad()
+    def gather_weights(self, layer_idx, dst: torch.Tensor):
+        """Window mode: all-gather the bf16 slices of a layer into `dst` (>= shard * world elements)
+        on the current stream."""
+        st = self.layers[layer_idx]
+        if st.shard == 0:
+            return None
+        return dist.all_gather_into_tensor(dst[: st.shard * self.world_size], st.bf16_shard)
 
     # ---- synchronisation ---------------------------------------------------------------------
     def barrier(self):
@@ -328,19 +371,42 @@ class SharedDataParallel:
             vec_ref = start + ((end - start) & ~15)         # where the reference call's tail begins
             vec_local = min(max(vec_ref - a, 0), k)
             with torch.cuda.device(self.device):
-                _lib.check(self._lib.sf_adam_step_sharded(
-                    C.byref(sc), state.params[lo:lo + k].data_ptr(), self._peer_ptrs(slot, a), self.world_size,
-                    self._gcode, state.exp_avg[lo:lo + k].data_ptr(), state.exp_avg_sq[lo:lo + k].data_ptr(),
-                    state.bf16[a:b].data_ptr(), k, vec_local, torch.cuda.current_stream().cuda_stream))
+                stream = torch.cuda.current_stream().cuda_stream
+                if state.bf16 is None:
+                    _lib.check(self._lib.sf_adam_step_sharded(
+                        C.byref(sc), state.params[lo:lo + k].data_ptr(), self._peer_ptrs(slot, a), self.world_size,
+                        self._gcode, state.exp_avg[lo:lo + k].data_ptr(), state.exp_avg_sq[lo:lo + k].data_ptr(),
+                        state.bf16_shard[lo:lo + k].data_ptr(), k, vec_local, stream))
+                elif state.peer_bf16 is not None:
+                    outs = (C.c_void_p * self.world_size)(*[base + 2 * a for base in state.peer_bf16])
+                    _lib.check(self._lib.sf_adam_step_sharded_push(
+                        C.byref(sc), state.params[lo:lo + k].data_ptr(), self._peer_ptrs(slot, a), outs,
+                        self.world_size, self._gcode, state.exp_avg[lo:lo + k].data_ptr(),
+                        state.exp_avg_sq[lo:lo + k].data_ptr(), k, vec_local, stream))
+                else:
+                    _lib.check(self._lib.sf_adam_step_sharded(
+                        C.byref(sc), state.params[lo:lo + k].data_ptr(), self._peer_ptrs(slot, a), self.world_size,
+                        self._gcode, state.exp_avg[lo:lo + k].data_ptr(), state.exp_avg_sq[lo:lo + k].data_ptr(),
+                        state.bf16[a:b].data_ptr(), k, vec_local, stream))
         if gather:
             self.all_gather_params(layer_idx)
 
     @torch.no_grad()
-    def all_gather_params(self, layer_idx, async_op: bool = False):
+    def all_gather_params(self, layer_idx, async_op: bool = False, force_nccl: bool = False):
         """All-gather the bf16 slices into every rank's full-layer buffer (in place).  Its
         completion on a rank also means every rank has finished reading that rank's gradients."""
         state = self.layers[layer_idx]
         if state.shard == 0:
+            return None
+        if state.bf16 is None:
+            # window mode: nothing to publish now, but the gradients of this layer may only be
+            # overwritten once every rank has finished reading them
+            self.stream_barrier()
+            return None
+        if state.peer_bf16 is not None and not force_nccl:
+            # the update kernels already stored every slice everywhere; once every rank's stream
+            # has passed this point all of those stores have completed
+            self.stream_barrier()
             return None
         mine = state.bf16[self.rank * state.shard:(self.rank + 1) * state.shard]
         return dist.all_gather_into_tensor(state.bf16, mine, async_op=async_op)
@@ -359,7 +425,7 @@ class SharedDataParallel:
             adam.step_chunk(state.params[:k], mine[:k], state.exp_avg[:k], state.exp_avg_sq[:k], param_group,
                             state.bf16[state.start:state.end])
         if gather:
-            self.all_gather_params(layer_idx)
+            self.all_gather_params(layer_idx, force_nccl=True)
 
     def close(self):
         """Release local resources after all ranks have drained their work."""
@@ -370,6 +436,9 @@ class SharedDataParallel:
         self.ctl.barrier()
         self.layers.clear()
         self._free_exchange()
+        for base, peers in self._weight_allocs:
+            self._shared_free(base, peers)
+        self._weight_allocs = []
         self._cap = 0
         self.ctl.close()
 
@@ -383,11 +452,11 @@ class ShardedLayerAdam:
 
     def __init__(self, numel: int, device, mode: str = "fused", grad_slots: int = 3, **hp):
         from .layer_adam import LayerAdam
-        if mode not in ("fused", "nccl"):
-            raise ValueError("mode must be 'fused' or 'nccl'")
+        if mode not in ("fused", "fused_ag", "nccl"):
+            raise ValueError("mode must be 'fused', 'fused_ag' or 'nccl'")
         self.mode = mode
         self.dp = SharedDataParallel(chunk_numel=max(int(numel), 1), dtype=torch.bfloat16, device=device,
-                                     exchange_slots=grad_slots)
+                                     exchange_slots=grad_slots, push_weights=(mode == "fused"))
         self.adam = LayerAdam(**hp)
         self.state = self.dp.register_layer(0, numel)
         self.numel = int(numel)
@@ -400,12 +469,15 @@ class ShardedLayerAdam:
 
     def describe(self) -> str:
         if self.mode == "fused":
+            return ("one kernel: peer-read fp32 rank-order gradient mean + Adam + bf16 weights pushed to every rank "
+                    "over NVLink, stream barriers before and after")
+        if self.mode == "fused_ag":
             return "fused peer-read fp32 rank-order mean + Adam kernel over NVLink, NCCL bf16 all-gather"
         return "NCCL bf16 reduce-scatter (avg), Adam kernel, NCCL bf16 all-gather"
 
     def step(self, k: int = 0):
         self.group["step"] += 1
-        if self.mode == "fused":
+        if self.mode in ("fused", "fused_ag"):
             self.dp.fused_update(0, self.adam, self.group, slot=k)
         else:
             self.dp.nccl_update(0, self.adam, self.group, slot=k)
@@ -437,7 +509,12 @@ class ShardedLayerAdam:
             g = self.group
             _lib.check(dp._lib.sf_adam_scalars(self.adam.optimizer_id, g["step"], g["lr"], g["betas"][0], g["betas"][1],
                                                g["eps"], g["weight_decay"], int(g["bias_correction"] == 1), C.byref(sc)))
-            if k > 0:
+            if k > 0 and st.peer_bf16 is not None:
+                outs = (C.c_void_p * dp.world_size)(*[base + 2 * st.start for base in st.peer_bf16])
+                _lib.check(dp._lib.sf_adam_step_sharded_push(
+                    C.byref(sc), st.params.data_ptr(), dp._peer_ptrs(0, st.start), outs, dp.world_size, dp._gcode,
+                    st.exp_avg.data_ptr(), st.exp_avg_sq.data_ptr(), k, k, torch.cuda.current_stream().cuda_stream))
+            elif k > 0:
                 _lib.check(dp._lib.sf_adam_step_sharded(
                     C.byref(sc), st.params.data_ptr(), dp._peer_ptrs(0, st.start), dp.world_size, dp._gcode,
                     st.exp_avg.data_ptr(), st.exp_avg_sq.data_ptr(), st.bf16[st.start:st.end].data_ptr(), k, k,
@@ -449,13 +526,13 @@ class ShardedLayerAdam:
             self.adam.step_chunk(st.params[:k], mine, st.exp_avg[:k], st.exp_avg_sq[:k], self.group,
                                  st.bf16[st.start:st.end])
 
-        return self._timed(fused if self.mode == "fused" else local, reps)
+        return self._timed(fused if self.mode in ("fused", "fused_ag") else local, reps)
 
     def breakdown(self, reps: int) -> dict:
         """Separate device times (ms, max over ranks) of the collectives around the kernel."""
         st, dp = self.state, self.dp
         out = {"stream_barrier_ms": self._timed(dp.stream_barrier, reps),
-               "all_gather_bf16_ms": self._timed(lambda: dp.all_gather_params(0), reps)}
+               "all_gather_bf16_ms": self._timed(lambda: dp.all_gather_params(0, force_nccl=True), reps)}
         if self.mode == "nccl":
             full = dp._exchange[0][: st.shard * dp.world_size]
             mine = full[dp.rank * st.shard:(dp.rank + 1) * st.shard]

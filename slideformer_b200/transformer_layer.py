@@ -57,6 +57,37 @@ class GradUnitPool:
         return u
 
 
+class WeightUnitPool:
+    """The parameter side of the reference's GPU cache units, used when a model's bf16 weights do
+    not fit next to the sharded optimizer state (70B on 8 GPUs): a ring of full-layer bf16
+    buffers that a layer's slices are all-gathered into shortly before the layer runs.  `free`
+    is recorded on the compute stream after the last kernel that read the unit."""
+
+    def __init__(self, num_units: int, numel: int, dtype, device):
+        self.units = []
+        for _ in range(num_units):
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(device))
+            self.units.append({"param": torch.empty(numel, dtype=dtype, device=device), "free": ev})
+        self._next = 0
+
+    def get(self):
+        u = self.units[self._next % len(self.units)]
+        self._next += 1
+        return u
+
+
+def _init_like_hf(name: str, shape, device, generator) -> torch.Tensor:
+    """Random init for a parameter that exists only on the meta device: N(0, 0.02) weights, unit
+    norm scales, zero biases (the Hugging Face defaults for the families handled here)."""
+    leaf = name.rsplit(".", 1)[-1]
+    if leaf == "bias":
+        return torch.zeros(shape, dtype=torch.float32, device=device)
+    if len(shape) == 1:
+        return torch.ones(shape, dtype=torch.float32, device=device)
+    return torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=generator)
+
+
 class OffloadLayerWrapper(nn.Module):
     """Base class: owns one unit's flat fp32 master weights, its permanent bf16 weights and the
     scheduling of its optimizer step."""
@@ -66,7 +97,8 @@ class OffloadLayerWrapper(nn.Module):
                  opt_stream: Optional[torch.cuda.Stream] = None, skip_params: Optional[set] = None,
                  tied_param: Optional[nn.Parameter] = None, enable_timing: bool = False, is_last_layer: bool = False,
                  layer_optimizer=None, dtype: torch.dtype = torch.bfloat16, state_device: str = "hbm",
-                 shared_dp=None, update_chunk: int = UPDATE_CHUNK_SIZE):
+                 shared_dp=None, update_chunk: int = UPDATE_CHUNK_SIZE, weight_pool: Optional[WeightUnitPool] = None,
+                 comm_stream: Optional[torch.cuda.Stream] = None, init_seed: int = 0):
         super().__init__()
         if layer_optimizer is None:
             raise RuntimeError("a shared LayerAdam must be provided")
@@ -93,16 +125,34 @@ class OffloadLayerWrapper(nn.Module):
         self._pending = 0          # parameters whose gradient has not been accumulated yet
         self.timings: Dict[str, List] = {"parameter_update": []}
 
+        self.weight_pool = weight_pool
+        self.comm_stream = comm_stream
+        self.weights_ready = torch.cuda.Event()
+        self._wunit = None
+        if weight_pool is not None and (shared_dp is None or tied_param is not None):
+            raise ValueError("the weight window needs sharded state (shared_dp) and untied embeddings")
+
+        # parameters that exist only on the meta device are created here, directly in their final place
+        gen = torch.Generator(device=device).manual_seed(1000003 * init_seed + layer_idx)
+        meta_init = {}
+        for n_, p_ in list(self.layer.named_parameters()):
+            if p_.is_meta and p_ not in self.skip_params:
+                owner_name, _, leaf = n_.rpartition(".")
+                owner = self.layer.get_submodule(owner_name) if owner_name else self.layer
+                newp = nn.Parameter(torch.empty(0, dtype=dtype, device=device), requires_grad=p_.requires_grad)
+                meta_init[id(newp)] = (n_, tuple(p_.shape))
+                owner._parameters[leaf] = newp
         self._managed_named_params = [(n, p) for n, p in self.layer.named_parameters() if p not in self.skip_params]
-        self.total_size = sum(p.numel() for _, p in self._managed_named_params)
+        shapes = {n_: (meta_init[id(p_)][1] if id(p_) in meta_init else tuple(p_.shape)) for n_, p_ in self._managed_named_params}
+        self.total_size = sum(int(torch.Size(sh).numel()) for sh in shapes.values())
         n = self.total_size
 
         # ---- storage: fp32 masters (+ moments in the optimizer) and permanent bf16 weights ----
         if shared_dp is not None:
-            st = shared_dp.register_layer(layer_idx, n)
+            st = shared_dp.register_layer(layer_idx, n, resident_bf16=weight_pool is None)
             self._dp_state = st
             self._params_flat = st.params                      # this rank's fp32 slice
-            self._bf16_flat = st.bf16[:n]                      # full layer, all-gather target
+            self._bf16_flat = st.bf16[:n] if st.bf16 is not None else None   # full layer, or None in window mode
             self._dp_group = None
         else:
             self._dp_state = None
@@ -119,17 +169,25 @@ class OffloadLayerWrapper(nn.Module):
             off = 0
             full_fp32 = torch.empty(n, dtype=torch.float32, device=device) if shared_dp is not None else None
             for name, p in self._managed_named_params:
-                k = p.numel()
-                self._param_maps[name] = (off, p.shape, k)
-                src = p.data.detach().to(device=device, dtype=torch.float32).reshape(-1)
+                shape = torch.Size(shapes[name])
+                k = shape.numel()
+                self._param_maps[name] = (off, shape, k)
+                if id(p) in meta_init:
+                    src = _init_like_hf(name, shape, device, gen).to(dtype).float().reshape(-1)
+                else:
+                    src = p.data.detach().to(device=device, dtype=torch.float32).reshape(-1)
                 if shared_dp is not None:
                     full_fp32[off:off + k].copy_(src)
                 else:
                     self._params_flat[off:off + k].copy_(src, non_blocking=True)
-                self._bf16_flat[off:off + k].copy_(src)
-                p.data = self._bf16_flat[off:off + k].view(p.shape)   # the weights the layer computes with
+                if self._bf16_flat is not None:
+                    self._bf16_flat[off:off + k].copy_(src)
+                    p.data = self._bf16_flat[off:off + k].view(shape)   # the weights the layer computes with
+                else:
+                    p.data = torch.empty(0, dtype=dtype, device=device)  # pointed into a window unit on demand
                 p.grad = None
                 off += k
+                del src
             if shared_dp is not None:
                 shared_dp.load_full_params(layer_idx, full_fp32)
                 del full_fp32
@@ -143,7 +201,7 @@ class OffloadLayerWrapper(nn.Module):
                 self.layer_optimizer.add_layer_params(layer_idx, self._master_views, self._bf16_views)
         for module in layer.modules():   # constants stay on the compute device (transformer_layer.py:148-152)
             for bname, buf in module.named_buffers(recurse=False):
-                if buf is not None and buf.device != device:
+                if buf is not None and not buf.is_meta and buf.device != device:
                     module._buffers[bname] = buf.to(device)
         for _, p in self._managed_named_params:
             if p.requires_grad:
@@ -154,6 +212,8 @@ class OffloadLayerWrapper(nn.Module):
         """Forward needs nothing (the bf16 weights are resident).  For backward: take the next
         gradient unit, wait until the optimizer has released it, zero it and point every
         parameter's .grad into it, so autograd accumulates straight into the flat buffer."""
+        if self.weight_pool is not None and self._wunit is None and not (is_bwd and isinstance(self, EmbeddingWrapper)):
+            self._acquire_weights()
         if not is_bwd or self._unit is not None:
             return
         unit = self.grad_pool.get()
@@ -169,8 +229,33 @@ class OffloadLayerWrapper(nn.Module):
                 self._pending += 1
         self._unit = unit
 
+    def _acquire_weights(self):
+        """Window mode: all-gather this unit's bf16 slices into the next window unit on the
+        communication stream (behind the unit's last optimizer step and the unit's previous
+        reader) and point the parameters into it (the counterpart of the reference's H2D task,
+        transformer_layer.py:273-335)."""
+        unit = self.weight_pool.get()
+        cs = self.comm_stream
+        with torch.cuda.stream(cs):
+            cs.wait_event(unit["free"])
+            if self._update_recorded:
+                cs.wait_event(self.update_done)
+            self.shared_dp.gather_weights(self.layer_idx, unit["param"])
+            self.weights_ready.record(cs)
+        for name, p in self._managed_named_params:
+            off, shape, k = self._param_maps[name]
+            p.data = unit["param"][off:off + k].view(shape)
+        self._wunit = unit
+
     def wait_for_h2d(self):
-        return None
+        if self._wunit is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.weights_ready)
+
+    def release_weights(self):
+        """The compute stream is done with this unit's window buffer."""
+        if self._wunit is not None:
+            self._wunit["free"].record(torch.cuda.current_stream(self.device))
+            self._wunit = None
 
     def to_offload_async(self, is_bwd: bool = False, prev_update=None):
         """Backward: mark the gradients complete on the compute stream (the counterpart of the
@@ -187,10 +272,12 @@ class OffloadLayerWrapper(nn.Module):
         self._pending -= 1
         if self._pending == 0:
             self.to_offload_async(is_bwd=True)
+            self.release_weights()
             self.update_params()
 
     def flush(self):
         """Run the update for a unit whose backward finished without touching every parameter."""
+        self.release_weights()
         if self._unit is not None:
             self.to_offload_async(is_bwd=True)
             self.update_params()
@@ -251,6 +338,8 @@ class OffloadLayerWrapper(nn.Module):
     def master_params_full(self) -> torch.Tensor:
         """Flat fp32 master weights on the device (for saving); sharded state is gathered from bf16."""
         if self.shared_dp is not None:
+            if self._bf16_flat is None:
+                raise NotImplementedError("gathering fp32 masters from window-mode shards is not implemented")
             return self._bf16_flat.float()
         return self._params_flat.to(self.device)
 

@@ -110,6 +110,13 @@ def test_error_codes_without_gpu(lib):
     assert lib.sf_adam_update(77, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, None, None, 0, None, None, None, 0, None) == 0
     assert lib.sf_adam_step_sharded(C.byref(s), None, None, 0, 0, None, None, None, 0, 0, None) == _lib.SF_ERR_ARG
     assert lib.sf_adam_step_sharded(C.byref(s), None, None, 17, 0, None, None, None, 0, 0, None) == _lib.SF_ERR_ARG
+    assert lib.sf_adam_step_sharded_push(C.byref(s), None, None, None, 0, 0, None, None, 0, 0, None) == _lib.SF_ERR_ARG
+    assert lib.sf_adam_step_sharded_push(C.byref(s), None, None, None, 2, 9, None, None, 0, 0, None) == _lib.SF_ERR_DTYPE
+    assert lib.sf_adam_step_sharded_push(C.byref(s), None, None, None, 2, 0, None, None, 16, 16, None) == _lib.SF_ERR_NULL
+    assert lib.sf_dp_mean(None, 2, 0, None, 16, None) == _lib.SF_ERR_NULL
+    assert lib.sf_dp_mean(None, 2, 0, None, 0, None) == 0
+    assert lib.sf_adam_update_dp_static(77, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, None, None, 2, 0, None, None, None,
+                                        lib.sf_static_scratch_max_elems() + 1, None) == _lib.SF_ERR_SIZE
     assert lib.sf_adam_update_host(77, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, None, None, 0, 0, None, None, None,
                                    0, 24, 0, None, 0, None) == _lib.SF_ERR_ARG  # chunk not a multiple of 16
     assert lib.sf_adam_host_scratch_bytes(1024, 0, 1) == 2 * (3 * 4096 + 2048)

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 HP = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
 
 
-def _worker(rank, world, path, out_dir):
+def _worker(rank, world, path, mode):
     import torch.distributed as dist
     from oracle import oracle as O
     from slideformer_b200.model_compat import build_random_model
@@ -29,14 +29,36 @@ def _worker(rank, world, path, out_dir):
     dist.init_process_group("nccl", init_method=f"file://{path}", rank=rank, world_size=world, device_id=dev)
     try:
         dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=2, timeout_seconds=60)
+        if mode == "meta":
+            # skeleton on the meta device, weights created per unit inside the engine, window mode
+            model = build_random_model("llama-tiny", dev, torch.bfloat16, seed=3, meta=True)
+            eng = SlideFormerOffloader(model, dev, torch.bfloat16, enable_timing=False, enable_memory_stats=False,
+                                       optimizer_kwargs=dict(HP), auto_backward_in_forward=True, shared_dp=dp,
+                                       weight_window=True)
+            gen = torch.Generator().manual_seed(100 + rank)
+            losses = []
+            for step in range(4):
+                ids = torch.randint(0, eng.config.vocab_size, (2, 32), generator=torch.Generator().manual_seed(7)).to(dev)
+                losses.append(float(eng(ids, labels=ids).loss.detach()))
+            assert all(np.isfinite(losses)) and losses[-1] < losses[0], losses   # same batch every step: loss falls
+            dp.barrier()
+            dp.close()
+            return
         model = build_random_model("llama-tiny", dev, torch.bfloat16, seed=3)
+        init_full = {}
         eng = SlideFormerOffloader(model, dev, torch.bfloat16, enable_timing=False, enable_memory_stats=False,
-                                   optimizer_kwargs=dict(HP), auto_backward_in_forward=False, shared_dp=dp)
+                                   optimizer_kwargs=dict(HP), auto_backward_in_forward=False, shared_dp=dp,
+                                   weight_window=(mode == "window"))
         units = eng.transformer_layers
         # expected state, full layers, kept on every rank
         exp = {}
         for u in units:
-            full = u._bf16_flat.float().cpu().numpy().copy()   # masters were created from the bf16 init
+            if mode == "window":
+                tmp = torch.empty(u._dp_state.shard * world, dtype=torch.bfloat16, device=dev)
+                dp.gather_weights(u.layer_idx, tmp)
+                full = tmp[: u.total_size].float().cpu().numpy().copy()
+            else:
+                full = u._bf16_flat.float().cpu().numpy().copy()   # masters were created from the bf16 init
             n = u.total_size
             exp[u.layer_idx] = [full, np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.uint16)]
         orc = O.OracleAdam(HP["lr"], *HP["betas"], HP["eps"], HP["weight_decay"], True)
@@ -72,16 +94,24 @@ def _worker(rank, world, path, out_dir):
                 k = st.end - st.start
                 assert np.array_equal(st.params[:k].cpu().numpy().view(np.uint32), p[st.start:st.end].view(np.uint32)), (step, idx)
                 assert np.array_equal(st.exp_avg[:k].cpu().numpy().view(np.uint32), m[st.start:st.end].view(np.uint32))
-                assert np.array_equal(u._bf16_flat.view(torch.int16).cpu().numpy().view(np.uint16), o), (step, idx)
+                if mode == "window":
+                    got = st.bf16_shard[:k].view(torch.int16).cpu().numpy().view(np.uint16)
+                    assert np.array_equal(got, o[st.start:st.end]), (step, idx)
+                else:
+                    assert np.array_equal(u._bf16_flat.view(torch.int16).cpu().numpy().view(np.uint16), o), (step, idx)
         dp.barrier()
         dp.close()
     finally:
         dist.destroy_process_group()
 
 
-def test_sharded_engine_two_ranks():
+@pytest.mark.parametrize("mode", ["resident", "window", "meta"])
+def test_sharded_engine_two_ranks(mode):
+    """resident: every rank keeps all bf16 layers (weights pushed by the update kernel);
+    window: only bf16 slices are kept and layers are all-gathered into window units on demand;
+    meta: window mode on a model whose weights are created per unit (never whole on one GPU)."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(_worker, args=(2, os.path.join(d, "rdv"), d), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, os.path.join(d, "rdv"), mode), nprocs=2, join=True)

@@ -101,10 +101,13 @@ def _worker(rank, world, path, scenario):
                             assert np.array_equal(got, O.f32_to_bf16(p))
                 dp.barrier()
                 dp.close()
-        elif scenario == "medium":
+        elif scenario in ("medium", "medium_allgather"):
             n = 1_000_003
             hp = (1e-5, 0.9, 0.999, 1e-8, 0.01)
-            dp = SharedDataParallel(chunk_numel=n, dtype=torch.bfloat16, timeout_seconds=60)
+            # default: the update kernel pushes the bf16 weights to every rank; otherwise NCCL all-gather
+            dp = SharedDataParallel(chunk_numel=n, dtype=torch.bfloat16, timeout_seconds=60,
+                                    push_weights=(scenario == "medium"))
+            assert (dp.register_layer(7, 64).peer_bf16 is not None) == (scenario == "medium")
             adam = LayerAdam(lr=hp[0], betas=hp[1:3], eps=hp[3], weight_decay=hp[4])
             orc = O.OracleAdam(*hp, True)
             st = dp.register_layer(0, n)
@@ -192,9 +195,10 @@ def test_reference_dp_sequence_sharded(world, scenario):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_medium_layer_fused_and_nccl(world):
+@pytest.mark.parametrize("scenario", ["medium", "medium_allgather"])
+def test_medium_layer_fused_and_nccl(world, scenario):
     _need(world)
-    _run(world, "medium")
+    _run(world, scenario)
 
 
 def test_host_failure_reaches_every_rank():
