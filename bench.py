@@ -434,7 +434,7 @@ def main_b200(args):
             del sh
         gc.collect()
         torch.cuda.empty_cache()
-        jobs = [("gpt2-small", 10, 3, "hbm"), ("llama3.1-8b", 4, 2, "hbm")]
+        jobs = [("gpt2-small", 20, 5, "hbm"), ("llama3.1-8b", 4, 2, "hbm")]
         if args.finetune == "full" and world == 1:
             jobs.append(("llama3.1-8b", 3, 1, "host"))
         finetune = []

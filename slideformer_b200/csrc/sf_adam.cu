@@ -222,6 +222,7 @@ __device__ __forceinline__ void st8(float* a, const f8& r)
 
 // Gradient sources.  `load4` returns 4 consecutive gradients as floats.
 struct GradBf16 {
+    static constexpr bool kPeer = false;
     const uint16_t* g;
     template <int HINT>
     __device__ __forceinline__ void load4(uint64_t i, float (&o)[4]) const
@@ -235,6 +236,7 @@ struct GradBf16 {
     __device__ __forceinline__ float load1(uint64_t i) const { return bf16_bits_to_f32(g[i]); }
 };
 struct GradF32 {
+    static constexpr bool kPeer = false;
     const float* g;
     template <int HINT>
     __device__ __forceinline__ void load4(uint64_t i, float (&o)[4]) const
@@ -250,6 +252,7 @@ struct GradF32 {
 // zero accumulator, add rank 0..world-1, true division by world.
 template <typename ELT>
 struct GradPeers {
+    static constexpr bool kPeer = true;
     const ELT* g[SF_MAX_WORLD];
     int world;
     float fworld;
@@ -326,8 +329,8 @@ adam_scalar_kernel(K c, float* p, GS gs, float* m, float* v, uint16_t* out, uint
 // U * 56 bytes per thread in flight.
 //   nvec    = elements handled here, a multiple of 4, all below vec_n (body arithmetic)
 //   [nvec, n) is finished by the last CTA with scalar accesses.
-template <typename GS, int MODE, bool OUT, int HINT, int U, int THREADS>
-__global__ void __launch_bounds__(THREADS)
+template <typename GS, int MODE, bool OUT, int HINT, int U, int THREADS, int MINB = 1>
+__global__ void __launch_bounds__(THREADS, MINB)
 adam_vec4_kernel(K c, float* __restrict__ p, GS gs, float* __restrict__ m, float* __restrict__ v,
                  uint16_t* __restrict__ out, uint64_t nvec, uint64_t n, uint64_t vec_n)
 {
@@ -600,13 +603,17 @@ int launch_vec4(const K& c, int mode, float* p, const GS& gs, float* m, float* v
     return dispatch_mode_out(mode, out != nullptr, [&](auto MODE, auto OUT) -> int {
         constexpr int M = decltype(MODE)::value;
         constexpr bool O = decltype(OUT)::value;
-        constexpr int U = 2, T = 256;
+        // Local gradients: two 4-element groups per thread at half occupancy is the fastest HBM
+        // shape.  Peer-mapped gradients: one group per thread at full occupancy (32 registers)
+        // hides the NVLink read latency (measured with the push kernel, which shares the shape).
+        constexpr bool PEER = GS::kPeer;
+        constexpr int U = PEER ? 1 : 2, T = 256, MINB = PEER ? 8 : 1;
         uint64_t ntiles = (nvec + (uint64_t)T * 4 * U - 1) / ((uint64_t)T * 4 * U);
         int grid = grid_for(ntiles, di.sms, cps);
         if (hint)
-            adam_vec4_kernel<GS, M, O, 1, U, T><<<grid, T, 0, st>>>(c, p, gs, m, v, out, nvec, n, vec_n);
+            adam_vec4_kernel<GS, M, O, 1, U, T, MINB><<<grid, T, 0, st>>>(c, p, gs, m, v, out, nvec, n, vec_n);
         else
-            adam_vec4_kernel<GS, M, O, 0, U, T><<<grid, T, 0, st>>>(c, p, gs, m, v, out, nvec, n, vec_n);
+            adam_vec4_kernel<GS, M, O, 0, U, T, MINB><<<grid, T, 0, st>>>(c, p, gs, m, v, out, nvec, n, vec_n);
         return check_launch("adam_vec4_kernel");
     });
 }
