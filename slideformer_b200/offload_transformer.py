@@ -218,5 +218,13 @@ class SlideFormerOffloader(nn.Module):
         """Write HF-format weights cast to the compute dtype (offload_transformer.py:593-597).  The
         live parameters already are the bf16 weights, so the model saves itself."""
         self.wait_for_completion()
-        self.base_model.save_pretrained(output_dir)
+        if self.weight_window:
+            raise NotImplementedError("saving from window-mode shards is not implemented")
+        # every parameter is a view into its unit's flat buffer; hand the serializer independent copies
+        state, seen = {}, {}
+        for name, value in self.base_model.state_dict(keep_vars=True).items():
+            if id(value) not in seen:
+                seen[id(value)] = value.detach().clone()
+            state[name] = seen[id(value)]
+        self.base_model.save_pretrained(output_dir, state_dict=state)
         return output_dir

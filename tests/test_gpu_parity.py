@@ -1,7 +1,7 @@
 """Parity of the CUDA path with the CPU oracle and the reference's golden vectors.
 
 Every compute call goes through the C ABI (directly, or through LayerAdam which does nothing
-but marshal pointers).  Tolerance: 0 ulp.  north_star allows 2 ulp on p / m / v and asks for a
+but marshal pointers).  Tolerance: 0 ulp.  The specification allows 2 ulp on p / m / v and asks for a
 bit-exact bf16 copy wherever the fp32 results agree; these tests assert bit equality of all
 four outputs, and NaN-ness where the result is a NaN (payloads are not compared).
 """
