@@ -364,6 +364,18 @@ def main_b200(args):
                 "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs, burst copy)" if which == "measured" else "fallback 6650 GB/s",
                 "kernel": "adam_vec4_kernel", "kernel_ms": kern_ms, "bytes_per_launch": hbm_bytes_per_launch,
                 "frac_of_nominal_8000": achieved / 8000.0}
+    if world > 1 and args.dp_mode == "fused":
+        # The fused kernel is bound by NVLink, not HBM: per launch every GPU receives the (N-1)
+        # peer gradient slices it pulls plus the (N-1) bf16 slices its peers push into it, and
+        # sends as much.  Peak: the 770 GB/s per direction a peer copy reaches on this pool.
+        link_bytes = 2 * (world - 1) * sh.shard_numel * 2
+        link = link_bytes / (kern_ms * 1e-3) / 1e9
+        roofline = {"bound": "nvlink", "achieved": link, "peak": 770.0, "unit": "GB/s", "frac": link / 770.0,
+                    "traffic": None, "peak_source": "measured peer copy, 770 GB/s per direction per GPU",
+                    "kernel": "adam_vec4_push_kernel", "kernel_ms": kern_ms, "bytes_per_launch": link_bytes,
+                    "note": "bytes received (= sent) per GPU per launch over NVLink",
+                    "hbm": {"achieved": achieved, "peak": peak, "frac": achieved / peak,
+                            "bytes_per_launch": hbm_bytes_per_launch}}
 
     # ---- end to end through the public API with host buffers -----------------------------------
     e2e = None

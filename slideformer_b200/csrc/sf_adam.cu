@@ -892,7 +892,11 @@ int sf_adam_step_sharded_push(const SfAdamScalars* s, float* p, const void* cons
     const uint64_t nvec = a16 ? ((vec_n < n ? vec_n : n) & ~(uint64_t)3) : 0;
     // Launch shape measured on two NVLink-connected B200s: one 4-element group per thread and
     // full occupancy (256 threads x 8 CTAs per SM, 32 registers) hides the peer-read latency best
-    // (0.65 ms for a 109 M-element slice against 1.44 ms for the single-GPU shape U=2 at half occupancy).
+    // (0.65 ms for a 109 M-element slice against 1.44 ms for the single-GPU shape U=2 at half
+    // occupancy).  At 0.65 ms each GPU receives 436 MB (its pulls plus the peer's pushes) and sends
+    // as much: about 675 GB/s per direction, close to the 770 GB/s a peer copy reaches, so the
+    // kernel is NVLink-bound; 8-element-per-thread variants with 128-bit peer accesses measured
+    // the same.
     constexpr int U = 1, T = 256, MINB = 8;
     const uint64_t ntiles = (nvec + (uint64_t)T * 4 * U - 1) / ((uint64_t)T * 4 * U);
     const int grid = grid_for(ntiles, di.sms, 0);
