@@ -355,6 +355,8 @@ def main_b200(args):
     else:
         kern_ms = sh.time_kernel_only(R)
         extra.update(sh.breakdown(R))
+        # the same step seen from the data side: every rank contributed one full-layer gradient
+        extra["dp_gradient_gparams_per_s"] = world * value
         barrier()
     peak, which = measured_peak()
     achieved = hbm_bytes_per_launch / (kern_ms * 1e-3) / 1e9
