@@ -141,8 +141,10 @@ def build_random_model(name: str, device, dtype=torch.bfloat16, seed: int = 0, a
         with torch.device("meta" if meta else device):
             if family == "gpt2":
                 from transformers import GPT2Config, GPT2LMHeadModel
+                # "gelu_pytorch_tanh" is GPT-2's tanh-approximated GELU (HF's default "gelu_new") as one
+                # fused kernel instead of eight elementwise ones
                 cfg = GPT2Config(resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0, attn_implementation=attn_implementation,
-                                 use_cache=False, **spec)
+                                 use_cache=False, activation_function="gelu_pytorch_tanh", **spec)
                 model = GPT2LMHeadModel(cfg)
             else:
                 from transformers import LlamaConfig, LlamaForCausalLM
