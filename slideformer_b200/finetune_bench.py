@@ -77,6 +77,8 @@ def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int,
         dp.barrier()
     torch.cuda.synchronize()
     l0 = lib.sf_launch_count()
+    for u in engine.transformer_layers:
+        u.host_update_seconds = 0.0
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     a.record()
@@ -102,7 +104,8 @@ def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int,
                        "activation_checkpoint": activation_checkpoint, "weight_window": weight_window,
                        "parallelism": f"dp{world} sharded state" if dp is not None else "single GPU"},
             "model_tflops": flops / (ms * 1e-3) / 1e12, "params": sum(u.total_size for u in engine.transformer_layers),
-            "optimizer_ms_per_step": sum(upd.values()), "optimizer_ms_decoder_layer": upd.get(1),
+            "optimizer_ms_per_step": sum(upd.values()),
+            "optimizer_host_enqueue_ms_per_step": 1e3 * sum(u.host_update_seconds for u in engine.transformer_layers) / steps, "optimizer_ms_decoder_layer": upd.get(1),
             "gpu_launches": int(lib.sf_launch_count() - l0), "loss_first": losses[0] if losses else None,
             "loss_last": losses[-1], "build_seconds": build_s,
             "max_memory_gb": torch.cuda.max_memory_allocated(dev) / 2**30,

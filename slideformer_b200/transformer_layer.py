@@ -22,6 +22,7 @@ blocks inside a step.
 """
 from __future__ import annotations
 
+import time
 from collections import OrderedDict
 from typing import Any, Dict, List, Optional
 
@@ -124,6 +125,7 @@ class OffloadLayerWrapper(nn.Module):
         self._unit = None
         self._pending = 0          # parameters whose gradient has not been accumulated yet
         self.timings: Dict[str, List] = {"parameter_update": []}
+        self.host_update_seconds = 0.0   # host time spent enqueueing optimizer steps (not device time)
 
         self.weight_pool = weight_pool
         self.comm_stream = comm_stream
@@ -288,6 +290,7 @@ class OffloadLayerWrapper(nn.Module):
         unit, self._unit = self._unit, None
         if unit is None:
             return None
+        _h0 = time.perf_counter()
         n = self.total_size
         g = unit["grad"]
         opt = self.layer_optimizer
@@ -328,6 +331,7 @@ class OffloadLayerWrapper(nn.Module):
         self._update_recorded = True
         for _, p in self._managed_named_params:
             p.grad = None
+        self.host_update_seconds += time.perf_counter() - _h0
         return self.update_done
 
     def wait_for_update(self):
