@@ -55,6 +55,14 @@ def shard_range(numel: int, world: int, rank: int, align: int = SHARD_ALIGN):
     return a, b
 
 
+def slice_vec_n(call_start: int, call_end: int, a: int, b: int) -> int:
+    """Where the reference call over [call_start, call_end) switches from its 16-lane body to its
+    scalar tail (cpu_adam_impl.cpp:23-68), expressed relative to the slice [a, b) of that call:
+    the `vec_n` to pass to the kernel so that a call executed in pieces keeps the reference's bits."""
+    vec_ref = call_start + ((call_end - call_start) & ~15)
+    return min(max(vec_ref - a, 0), b - a)
+
+
 @dataclass
 class LayerState:
     """Per-layer state.  `params`, `exp_avg`, `exp_avg_sq` keep the reference's names but hold
@@ -368,8 +376,7 @@ class SharedDataParallel:
         a, b = max(start, state.start), min(end, state.end)
         if b > a:
             k, lo = b - a, a - state.start
-            vec_ref = start + ((end - start) & ~15)         # where the reference call's tail begins
-            vec_local = min(max(vec_ref - a, 0), k)
+            vec_local = slice_vec_n(start, end, a, b)
             with torch.cuda.device(self.device):
                 stream = torch.cuda.current_stream().cuda_stream
                 if state.bf16 is None:
