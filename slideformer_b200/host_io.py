@@ -37,7 +37,6 @@ class HostGradStepper:
                           for _ in range(2)]
         self.ev_in = [torch.cuda.Event() for _ in range(2)]
         self.ev_k = [torch.cuda.Event() for _ in range(2)]
-        self.ev_out = [torch.cuda.Event() for _ in range(2)]
 
     @torch.no_grad()
     def step(self, p: torch.Tensor, g_host: torch.Tensor, m: torch.Tensor, v: torch.Tensor,

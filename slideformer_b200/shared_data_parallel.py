@@ -353,10 +353,13 @@ class SharedDataParallel:
     # ---- the fused call --------------------------------------------------------------------------
     @torch.no_grad()
     def fused_update(self, layer_idx, adam, param_group: dict, start: int = 0, end: Optional[int] = None,
-                     local_grad: Optional[torch.Tensor] = None, slot: int = 0, gather: bool = True):
+                     local_grad: Optional[torch.Tensor] = None, slot: int = 0, gather: bool = True,
+                     barrier: bool = True):
         """Mean + Adam + bf16 cast in one kernel on this rank's part of [start, end), then (by
         default) the all-gather of the layer's bf16 weights.  `adam` is a LayerAdam (its scalar
-        state machine advances once per call, like one reference adam_update)."""
+        state machine advances once per call, like one reference adam_update).  barrier=False
+        skips the leading cross-rank stream barrier: correct for the second and later chunks of
+        a layer whose whole gradient was complete on every rank before the first chunk's barrier."""
         self.raise_if_failed()
         state = self.layers[layer_idx]
         end = state.numel if end is None else end
@@ -367,7 +370,8 @@ class SharedDataParallel:
         if local_grad is not None:
             self._validate(state, start, end, local_grad)
             self._stage(slot, start, end, local_grad)
-        self.stream_barrier()
+        if barrier:
+            self.stream_barrier()
         sc = _lib.SfAdamScalars()
         _lib.check(self._lib.sf_adam_scalars(adam.optimizer_id, int(param_group["step"]), param_group["lr"],
                                              param_group["betas"][0], param_group["betas"][1], param_group["eps"],

@@ -309,8 +309,10 @@ class OffloadLayerWrapper(nn.Module):
                 self._dp_state.step = self._dp_group["step"]
                 for cs in range(0, n, self.update_chunk):
                     ce = min(cs + self.update_chunk, n)
+                    # the unit's whole gradient is complete here on every rank once the first
+                    # chunk's barrier has passed, so later chunks need none
                     self.shared_dp.fused_update(self.layer_idx, opt, self._dp_group, cs, ce, slot=unit["slot"],
-                                                gather=False)
+                                                gather=False, barrier=(cs == 0))
                 self.shared_dp.all_gather_params(self.layer_idx)
             else:
                 group = opt.begin_chunk_step(self.layer_idx)
