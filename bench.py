@@ -37,12 +37,13 @@ HP = dict(lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
 WORKLOAD = "llama3.1-8b decoder layer, flat n=218112000, fp32 p/m/v + bf16 grad -> bf16 copy"
 METRIC = "LayerAdam Gparams/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
-# profiles/adam_vec4_kernel_llama8b_layer.md (n = 16,777,216): reads are 14.00 B/param, writes
-# are 14 B/param minus about 56 MB that is still dirty in L2 when the kernel ends (a constant,
-# it does not grow with n).  Scaled to a launch over `units` parameters.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised in
+# profiles/adam_vec4_kernel_llama8b_layer.md: at n = 218,112,000 reads are 3,053.7 MB
+# (14.00 B/param) and writes 2,993.5 MB, i.e. 14 B/param minus about 60 MB that is still dirty
+# in L2 when the kernel ends (the same shortfall, 53-57 MB, shows at n = 16,777,216: it does not
+# grow with n).  Scaled to a launch over `units` parameters.
 def ncu_traffic_bytes(units: int) -> float:
-    return 14.0 * units + max(14.0 * units - 56e6, 0.0)
+    return 14.0 * units + max(14.0 * units - 60e6, 0.0)
 
 
 _RESULT_FD = None
@@ -278,6 +279,8 @@ def main_b200(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
+    if args.variant >= 0 or args.ctas_per_sm >= 0:
+        _lib.check(lib.sf_set_tuning(args.variant, args.ctas_per_sm))
     n = args.n
     K, W = args.steps, max(3, args.warmup)
 
@@ -497,6 +500,9 @@ def main():
     ap.add_argument("--host-state", action="store_true", default=True)
     ap.add_argument("--no-host-state", dest="host_state", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--variant", type=int, default=-1,
+                    help="access pattern of the kernel (sf_set_tuning): 0 default caching, 1 streaming hints, 2 256-bit")
+    ap.add_argument("--ctas-per-sm", type=int, default=-1, help="0 = one tile per CTA, k > 0 = persistent grid")
     ap.add_argument("--finetune", default="all", choices=["none", "all", "full"],
                     help="also report fine-tune tokens/s of GPT-2 small and Llama-3.1-8B through the engine "
                          "(batch 8 x 1024 per GPU); 'full' adds the host-pinned-state mode at N=1")

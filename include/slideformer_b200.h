@@ -180,7 +180,9 @@ int sf_adam_update_dp_static(int id, uint64_t step, float lr, float beta1, float
  * chunk_elems must be a multiple of 16 (so every chunk but the last stays on the vector
  * body, like the reference's 32 Mi-element chunks, transformer_layer.py:26-27).  The scalar
  * state machine advances once (one reference call per chunk would take the pow() branch
- * from the second chunk on; pass per_chunk_scalars != 0 to reproduce that). */
+ * from the second chunk on; pass per_chunk_scalars != 0 to reproduce that).  All calls that
+ * target one device share one set of internal streams and events: issue them from one thread
+ * at a time. */
 size_t sf_adam_host_scratch_bytes(uint64_t chunk_elems, int g_dtype, int g_on_host);
 int sf_adam_update_host(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
                         float weight_decay, int bias_correction, float* p_host,
