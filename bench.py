@@ -387,7 +387,7 @@ def main_b200(args):
     if world == 1:
         g_host = [grads[k].cpu().pin_memory() for k in range(2)]
         out_host = torch.empty(n, dtype=torch.bfloat16).pin_memory()
-        stepper = HostGradStepper(opt, n, dev, chunk_numel=args.e2e_chunk)
+        stepper = HostGradStepper(opt, n, dev, chunk_numel=args.e2e_chunk, min_chunk_numel=args.e2e_min_chunk)
         E = max(3, min(K, 20))
         for i in range(3):
             group["step"] += 1
@@ -406,7 +406,8 @@ def main_b200(args):
         e2e = {"value": n / (e2e_ms * 1e-3) / 1e9, "unit": "Gparams/s", "h2d_bytes_per_step": 2 * n,
                "d2h_bytes_per_step": 2 * n, "ms_per_step": e2e_ms, "steps": E,
                "path": "HostGradStepper: pinned bf16 gradient -> HBM-resident LayerAdam.step_chunk -> pinned bf16 weights, "
-                       f"{args.e2e_chunk}-element chunks on three streams"}
+                       f"{len(stepper.chunks)} pieces of {args.e2e_min_chunk}..{args.e2e_chunk} elements "
+                       "(short at both ends) on three streams"}
         extra["pcie"] = measure_pcie(dev)
         # fully host-resident state (p, m, v and g in pinned host memory) streamed through the GPU
         if args.host_state:
@@ -497,6 +498,7 @@ def main():
     ap.add_argument("--n", type=int, default=N_LAYER, help="flat layer size (parity and sweep runs only)")
     ap.add_argument("--dp-mode", default="fused", choices=["fused", "fused_ag", "nccl"])
     ap.add_argument("--e2e-chunk", type=int, default=16 * 1024 * 1024)
+    ap.add_argument("--e2e-min-chunk", type=int, default=4 * 1024 * 1024)
     ap.add_argument("--host-state", action="store_true", default=True)
     ap.add_argument("--no-host-state", dest="host_state", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")

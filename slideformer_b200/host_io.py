@@ -16,19 +16,58 @@ import torch
 from .layer_adam import LayerAdam
 
 
+def chunk_schedule(numel: int, chunk: int, min_chunk: int):
+    """Cut [0, numel) into pieces that ramp up from `min_chunk` to `chunk` by doubling, stay at
+    `chunk`, and ramp down again.  The first upload and the last download are the only copies
+    that nothing overlaps, so short pieces at both ends shrink the pipeline's fill and drain time.
+    Every boundary is a multiple of 16 elements (each piece keeps the vector body / scalar tail
+    split of one reference call), except the end of the last piece."""
+    if chunk % 16 or min_chunk % 16 or min_chunk <= 0 or chunk < min_chunk:
+        raise ValueError("chunk sizes must be positive multiples of 16 with min_chunk <= chunk")
+    up, c = [], min_chunk
+    while c < chunk:
+        up.append(c)
+        c *= 2
+    pieces, pos = [], 0
+    ramp = sum(up)
+    if numel <= 2 * ramp + chunk:          # too small to ramp: plain equal chunks
+        while pos < numel:
+            pieces.append((pos, min(pos + chunk, numel)))
+            pos += chunk
+        return pieces
+    for c in up:
+        pieces.append((pos, pos + c))
+        pos += c
+    while numel - pos > ramp + chunk:
+        pieces.append((pos, pos + chunk))
+        pos += chunk
+    tail = numel - pos - ramp               # in (0, chunk]
+    pieces.append((pos, pos + tail - (tail % 16 if numel - (pos + tail) > 0 else 0)))
+    pos = pieces[-1][1]
+    for c in reversed(up):
+        end = min(pos + c, numel)
+        if end > pos:
+            pieces.append((pos, end))
+        pos = end
+    if pos < numel:
+        pieces.append((pos, numel))
+    return pieces
+
+
 class HostGradStepper:
     """Runs `LayerAdam.step_chunk` over a flat HBM-resident layer whose gradient is in pinned
     host memory, optionally returning the bf16 copy of the updated weights to pinned host
     memory.  Chunk k+1's upload, chunk k's kernel and chunk k-1's download run concurrently."""
 
     def __init__(self, opt: LayerAdam, numel: int, device, chunk_numel: int = 32 * 1024 * 1024,
-                 grad_dtype=torch.bfloat16):
+                 grad_dtype=torch.bfloat16, min_chunk_numel: int = None):
         if chunk_numel % 16:
             raise ValueError("chunk_numel must be a multiple of 16 so every chunk but the last stays on the vector body")
         self.opt = opt
         self.numel = int(numel)
         self.device = torch.device(device)
         self.chunk = int(chunk_numel)
+        self.chunks = chunk_schedule(self.numel, self.chunk, int(min_chunk_numel or chunk_numel))
         with torch.cuda.device(self.device):
             self.s_in = torch.cuda.Stream()
             self.s_k = torch.cuda.Stream()
@@ -49,10 +88,8 @@ class HostGradStepper:
         cur = torch.cuda.current_stream(self.device)
         for s in (self.s_in, self.s_k, self.s_out):
             s.wait_stream(cur)
-        nchunks = (n + self.chunk - 1) // self.chunk
-        for k in range(nchunks):
+        for k, (a, b) in enumerate(self.chunks):
             slot = k & 1
-            a, b = k * self.chunk, min((k + 1) * self.chunk, n)
             with torch.cuda.stream(self.s_in):
                 if k >= 2:
                     self.s_in.wait_event(self.ev_k[slot])  # the kernel of chunk k-2 has consumed this slot

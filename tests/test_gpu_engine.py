@@ -206,13 +206,13 @@ def test_host_grad_stepper_matches_oracle(oracle):
     out_host = torch.zeros(n, dtype=torch.bfloat16).pin_memory()
     opt = LayerAdam(**HP)
     orc = oracle.OracleAdam(*hp, True)
-    stepper = HostGradStepper(opt, n, DEV, chunk_numel=chunk)
+    stepper = HostGradStepper(opt, n, DEV, chunk_numel=chunk, min_chunk_numel=256)
+    assert stepper.chunks[0] == (0, 256) and stepper.chunks[-1][1] == n and len(stepper.chunks) > 6
     group = dict(opt.defaults, step=0)
     for step in (1, 2, 3):
         g = (torch.randn(n, generator=gen) * 1e-3).to(torch.bfloat16)
         gnp = g.view(torch.int16).numpy().view(np.uint16)
-        for cs in range(0, n, chunk):   # one reference call per chunk, like the reference's chunk consumer
-            ce = min(cs + chunk, n)
+        for cs, ce in stepper.chunks:   # one reference call per piece, like the reference's chunk consumer
             orc.adam_update(step, *hp, True, po[cs:ce], gnp[cs:ce], mo[cs:ce], vo[cs:ce], oo[cs:ce])
         group["step"] = step
         stepper.step(pd, g.pin_memory(), md, vd, od, out_host, group)

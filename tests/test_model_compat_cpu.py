@@ -69,3 +69,16 @@ def test_benchmark_layer_size_is_the_llama_8b_decoder_layer():
     h, kv, inter = spec["hidden_size"], spec["num_key_value_heads"] * (spec["hidden_size"] // spec["num_attention_heads"]), spec["intermediate_size"]
     n = 2 * h * h + 2 * h * kv + 3 * h * inter + 2 * h
     assert n == 218_112_000
+
+
+def test_chunk_schedule_covers_the_range_with_short_ends():
+    from slideformer_b200.host_io import chunk_schedule
+    for n, c, m in ((218_112_000, 16 << 20, 1 << 20), (20528, 4096, 256), (100, 4096, 16), (163847, 4096, 64), (1 << 20, 1 << 18, 1 << 14)):
+        p = chunk_schedule(n, c, m)
+        assert p[0][0] == 0 and p[-1][1] == n
+        assert all(a < b and a % 16 == 0 and b - a <= c for a, b in p)
+        assert all(p[i][1] == p[i + 1][0] for i in range(len(p) - 1))
+    p = chunk_schedule(218_112_000, 16 << 20, 1 << 20)
+    assert p[0][1] - p[0][0] == 1 << 20 and p[-1][1] - p[-1][0] == 1 << 20 and len(p) == 20
+    with pytest.raises(ValueError):
+        chunk_schedule(100, 24, 8)
