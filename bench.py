@@ -398,7 +398,8 @@ def main_b200(args):
         a.record()
         for i in range(E):
             group["step"] += 1
-            stepper.step(p, g_host[i & 1], m, v, out, out_host, group)
+            stepper.step(p, g_host[i & 1], m, v, out, out_host, group, join=False)
+        stepper.join()
         b.record()
         torch.cuda.synchronize()
         wall_ms = (time.perf_counter() - t0) * 1e3

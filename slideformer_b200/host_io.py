@@ -76,12 +76,17 @@ class HostGradStepper:
                           for _ in range(2)]
         self.ev_in = [torch.cuda.Event() for _ in range(2)]
         self.ev_k = [torch.cuda.Event() for _ in range(2)]
+        self.ev_out = [torch.cuda.Event() for _ in self.chunks]   # download of piece k finished
 
     @torch.no_grad()
     def step(self, p: torch.Tensor, g_host: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
-             bf16_dev: Optional[torch.Tensor], bf16_host: Optional[torch.Tensor], param_group: dict):
+             bf16_dev: Optional[torch.Tensor], bf16_host: Optional[torch.Tensor], param_group: dict,
+             join: bool = True):
         """One optimizer step.  p, m, v, bf16_dev: flat CUDA tensors; g_host, bf16_host: flat pinned
-        host tensors.  Returns after enqueueing; the caller's current stream waits for the end."""
+        host tensors.  Returns after enqueueing.  join=True makes the caller's current stream wait
+        for the end of the step.  With join=False the next step's uploads may start while this
+        step's downloads drain (every hazard between the two steps is covered by an event); call
+        `join()` before reading `bf16_host` or touching p, m, v from another stream."""
         n = self.numel
         if not g_host.is_pinned() or (bf16_host is not None and not bf16_host.is_pinned()):
             raise RuntimeError("host buffers must be pinned")
@@ -91,12 +96,14 @@ class HostGradStepper:
         for k, (a, b) in enumerate(self.chunks):
             slot = k & 1
             with torch.cuda.stream(self.s_in):
-                if k >= 2:
-                    self.s_in.wait_event(self.ev_k[slot])  # the kernel of chunk k-2 has consumed this slot
+                # the kernel that last read this staging slot (piece k-2, or a piece of the previous
+                # step) has finished; waiting on a never-recorded event is a no-op
+                self.s_in.wait_event(self.ev_k[slot])
                 self.g_dev[slot][: b - a].copy_(g_host[a:b], non_blocking=True)
                 self.ev_in[slot].record(self.s_in)
             with torch.cuda.stream(self.s_k):
                 self.s_k.wait_event(self.ev_in[slot])
+                self.s_k.wait_event(self.ev_out[k])   # the previous step's download of this piece is done
                 self.opt.step_chunk(p[a:b], self.g_dev[slot][: b - a], m[a:b], v[a:b], param_group,
                                     bf16_dev[a:b] if bf16_dev is not None else None)
                 self.ev_k[slot].record(self.s_k)
@@ -104,5 +111,12 @@ class HostGradStepper:
                 with torch.cuda.stream(self.s_out):
                     self.s_out.wait_event(self.ev_k[slot])
                     bf16_host[a:b].copy_(bf16_dev[a:b], non_blocking=True)
+                    self.ev_out[k].record(self.s_out)
+        if join:
+            self.join()
+
+    def join(self):
+        """Make the current stream wait for everything this stepper has enqueued."""
+        cur = torch.cuda.current_stream(self.device)
         cur.wait_stream(self.s_k)
         cur.wait_stream(self.s_out)

@@ -215,8 +215,9 @@ def test_host_grad_stepper_matches_oracle(oracle):
         for cs, ce in stepper.chunks:   # one reference call per piece, like the reference's chunk consumer
             orc.adam_update(step, *hp, True, po[cs:ce], gnp[cs:ce], mo[cs:ce], vo[cs:ce], oo[cs:ce])
         group["step"] = step
-        stepper.step(pd, g.pin_memory(), md, vd, od, out_host, group)
-        torch.cuda.synchronize()
+        # steps 1 and 2 are left to overlap; the last one is joined
+        stepper.step(pd, g.pin_memory(), md, vd, od, out_host, dict(group), join=(step == 3))
+    torch.cuda.synchronize()
     assert np.array_equal(_bits(pd), po.view(np.uint32))
     assert np.array_equal(_bits(md), mo.view(np.uint32)) and np.array_equal(_bits(vd), vo.view(np.uint32))
     assert np.array_equal(out_host.view(torch.int16).numpy().view(np.uint16), oo)
