@@ -1,143 +1,201 @@
-"""Single-node data-parallel fine-tuning entry point (one rank per GPU, state sharded 1/N).
+"""Data-parallel fine-tuning launcher: one rank per GPU, optimizer state sharded 1/N in HBM.
 
-    python -m slideformer_b200.main_dp --tiny                                   # one GPU smoke check
+    python -m slideformer_b200.main_dp --tiny                        # single GPU smoke run
     torchrun --nproc-per-node N -m slideformer_b200.main_dp --tiny [--tied] [--double-buffer]
-    torchrun --nproc-per-node N -m slideformer_b200.main_dp --model /path/to/checkpoint --tokens ids.pt
+    torchrun --nproc-per-node N -m slideformer_b200.main_dp --model CKPT_DIR --tokens ids.pt
 
-Counterpart of the reference's multi_gpu/scripts/main_dp.py (same flags where they still mean
-something; --cpu-threads is accepted and ignored because no CPU thread runs the optimizer).
-With --tiny it repeats the reference's smoke checks (main_dp.py:55-61,117-124): a random
-two-layer Llama, a few steps, then every unit's fp32 weights must be finite and changed and
-the optimizer step count must equal the number of completed steps.
+The command line follows the reference's multi_gpu/scripts/main_dp.py so existing job scripts
+keep working (`--cpu-threads` is accepted and ignored: no CPU thread runs the optimizer here).
+`--tiny` reproduces that script's self-check (main_dp.py:55-61,117-124): a random two-layer
+Llama is trained for a few steps, after which every unit's fp32 master weights must be finite
+and different from their initial values and each unit must have taken exactly one optimizer
+step per training step.
 """
 from __future__ import annotations
 
 import argparse
 import os
 import sys
+from dataclasses import dataclass
+from typing import Iterator, List, Optional
 
 import torch
 import torch.distributed as dist
-from torch.utils.data import DataLoader, DistributedSampler, TensorDataset
+
+TINY_SHAPE = dict(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=2)
 
 
-def main(argv=None):
-    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    source = parser.add_mutually_exclusive_group(required=True)
-    source.add_argument("--model", help="local Hugging Face checkpoint directory")
-    source.add_argument("--tiny", action="store_true", help="random tiny Llama with synthetic tokens, for smoke checks")
-    parser.add_argument("--tokens", help="torch.save file containing a 2-D int64 input_ids tensor")
-    parser.add_argument("--batch-size", type=int, default=1, help="sequences per rank")
-    parser.add_argument("--seq-length", type=int, default=32, help="synthetic sequence length for --tiny")
-    parser.add_argument("--steps", type=int, default=3)
-    parser.add_argument("--lr", type=float, default=1e-4)
-    parser.add_argument("--cpu-threads", type=int, default=1, help="accepted for compatibility; unused")
-    parser.add_argument("--chunk-numel", type=int, default=32 * 1024 * 1024)
-    parser.add_argument("--double-buffer", action="store_true")
-    parser.add_argument("--attn-implementation", choices=("eager", "sdpa", "flash_attention_2"), default="sdpa")
-    parser.add_argument("--tied", action="store_true", help="use tied embeddings with --tiny")
-    parser.add_argument("--save-model", help="save final model weights; optimizer resume is not supported")
-    args = parser.parse_args(argv)
-    if min(args.steps, args.batch_size, args.chunk_numel) < 1 or args.seq_length < 2:
-        parser.error("steps, batch-size and chunk-numel must be positive; seq-length must be >= 2")
-    if args.model and not args.tokens:
-        parser.error("--model requires --tokens; synthetic data is only used with --tiny")
+@dataclass
+class Ranks:
+    rank: int
+    world: int
+    device: torch.device
 
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    distributed = world > 1
-    if distributed:
-        dist.init_process_group("nccl", device_id=device)
-        if int(os.environ.get("LOCAL_WORLD_SIZE", world)) != world:
-            raise ValueError("This entry point supports a single node only")
-    rank = dist.get_rank() if distributed else 0
+    @property
+    def distributed(self) -> bool:
+        return self.world > 1
 
-    from transformers import AutoModelForCausalLM, LlamaConfig, LlamaForCausalLM
+
+def parse_args(argv=None) -> argparse.Namespace:
+    ap = argparse.ArgumentParser(prog="slideformer_b200.main_dp", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    what = ap.add_mutually_exclusive_group(required=True)
+    what.add_argument("--tiny", action="store_true", help="train a random two-layer Llama on synthetic tokens and self-check")
+    what.add_argument("--model", metavar="DIR", help="Hugging Face checkpoint directory on local disk")
+    ap.add_argument("--tokens", metavar="FILE", help="torch.save'd int64 tensor [num_sequences, seq_len] (required with --model)")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--batch-size", type=int, default=1, help="sequences per rank and step")
+    ap.add_argument("--seq-length", type=int, default=32, help="length of the synthetic sequences of --tiny")
+    ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--chunk-numel", type=int, default=1 << 25, help="elements per optimizer call")
+    ap.add_argument("--double-buffer", action="store_true", help="three gradient units instead of two")
+    ap.add_argument("--tied", action="store_true", help="--tiny with tied input/output embeddings")
+    ap.add_argument("--attn-implementation", default="sdpa", choices=("eager", "sdpa", "flash_attention_2"))
+    ap.add_argument("--save-model", metavar="DIR", help="write the final weights (optimizer state is not saved)")
+    ap.add_argument("--cpu-threads", type=int, default=1, help="ignored; kept for command-line compatibility")
+    ns = ap.parse_args(argv)
+    for name in ("steps", "batch_size", "chunk_numel"):
+        if getattr(ns, name) < 1:
+            ap.error(f"--{name.replace('_', '-')} must be at least 1")
+    if ns.seq_length < 2:
+        ap.error("--seq-length must be at least 2")
+    if ns.model and not ns.tokens:
+        ap.error("--model needs --tokens (synthetic tokens are only generated for --tiny)")
+    return ns
+
+
+def join_ranks() -> Ranks:
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world == 1:
+        return Ranks(0, 1, device)
+    if int(os.environ.get("LOCAL_WORLD_SIZE", world)) != world:
+        raise ValueError("all ranks must run on one node")
+    dist.init_process_group("nccl", device_id=device)
+    return Ranks(dist.get_rank(), world, device)
+
+
+def make_model(ns: argparse.Namespace):
+    torch.manual_seed(1234)   # identical initial weights on every rank
+    if ns.tiny:
+        from transformers import LlamaConfig, LlamaForCausalLM
+        cfg = LlamaConfig(**TINY_SHAPE, max_position_embeddings=max(128, ns.seq_length), attention_dropout=0.0,
+                          tie_word_embeddings=ns.tied, attn_implementation=ns.attn_implementation, use_cache=False)
+        return LlamaForCausalLM(cfg).to(torch.bfloat16)
+    from transformers import AutoModelForCausalLM
+    model = AutoModelForCausalLM.from_pretrained(ns.model, dtype=torch.bfloat16, attn_implementation=ns.attn_implementation)
+    model.config.use_cache = False
+    return model
+
+
+def load_sequences(ns: argparse.Namespace, vocab: int, world: int) -> torch.Tensor:
+    if not ns.tokens:
+        g = torch.Generator().manual_seed(4321)
+        return torch.randint(vocab, (ns.steps * world * ns.batch_size, ns.seq_length), generator=g)
+    seqs = torch.load(ns.tokens, map_location="cpu", weights_only=True)
+    good = isinstance(seqs, torch.Tensor) and seqs.dtype == torch.int64 and seqs.ndim == 2 and seqs.shape[1] >= 2
+    if not good:
+        raise ValueError("--tokens must hold a 2-D int64 tensor with at least two tokens per sequence")
+    if seqs.numel() == 0 or int(seqs.min()) < 0 or int(seqs.max()) >= vocab:
+        raise ValueError("token ids must be non-empty and inside the model's vocabulary")
+    return seqs
+
+
+def batches(seqs: torch.Tensor, ranks: Ranks, per_rank: int) -> Iterator[torch.Tensor]:
+    """Endless stream of this rank's batches: every epoch draws a fresh permutation (same on all
+    ranks) and rank r takes sequences r, r + world, ... of it, dropping the ragged end."""
+    group = per_rank * ranks.world
+    usable = (seqs.shape[0] // group) * group
+    if usable == 0:
+        raise ValueError("the token file is too small for one full batch on every rank")
+    epoch = 0
+    while True:
+        order = torch.randperm(seqs.shape[0], generator=torch.Generator().manual_seed(epoch))[:usable]
+        mine = order[ranks.rank::ranks.world]
+        for lo in range(0, mine.numel(), per_rank):
+            yield seqs[mine[lo:lo + per_rank]]
+        epoch += 1
+
+
+def all_ranks_finite(x: torch.Tensor, ranks: Ranks) -> bool:
+    flag = torch.isfinite(x.detach()).all().to(torch.int32)
+    if ranks.distributed:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
+
+
+def mean_over_ranks(x: torch.Tensor, ranks: Ranks) -> float:
+    y = x.detach().float().clone()
+    if ranks.distributed:
+        dist.all_reduce(y)
+        y /= ranks.world
+    return float(y.item())
+
+
+def owned_master_weights(engine) -> List[torch.Tensor]:
+    """The fp32 master weights this rank owns, one flat tensor per unit."""
+    out = []
+    for unit in engine.transformer_layers:
+        st = unit._dp_state
+        out.append(unit._params_flat[: (st.end - st.start) if st is not None else unit.total_size])
+    return out
+
+
+def self_check(engine, before: List[torch.Tensor], steps_done: int, dp) -> None:
+    for unit, old, new in zip(engine.transformer_layers, before, owned_master_weights(engine)):
+        if new.numel() and (torch.equal(old, new) or not bool(torch.isfinite(new).all())):
+            raise RuntimeError(f"unit {unit.layer_idx}: master weights unchanged or not finite after training")
+        taken = unit._dp_state.step if dp is not None else engine.layer_optimizer.param_groups[unit.layer_idx]["step"]
+        if taken != steps_done:
+            raise RuntimeError(f"unit {unit.layer_idx}: {taken} optimizer steps for {steps_done} training steps")
+
+
+def main(argv=None) -> int:
+    ns = parse_args(argv)
+    ranks = join_ranks()
     from slideformer_b200.offload_transformer import SlideFormerOffloader
     from slideformer_b200.shared_data_parallel import SharedDataParallel
 
-    torch.manual_seed(1234)
-    dtype = torch.bfloat16
-    if args.tiny:
-        config = LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
-                             num_attention_heads=4, num_key_value_heads=2,
-                             max_position_embeddings=max(128, args.seq_length), tie_word_embeddings=args.tied,
-                             attention_dropout=0.0, attn_implementation=args.attn_implementation)
-        base_model = LlamaForCausalLM(config).to(dtype=dtype)
-    else:
-        base_model = AutoModelForCausalLM.from_pretrained(args.model, dtype=dtype,
-                                                          attn_implementation=args.attn_implementation)
-    base_model.config.use_cache = False
-    vocab = base_model.config.vocab_size
-    if args.tokens:
-        tokens = torch.load(args.tokens, map_location="cpu", weights_only=True)
-        if not isinstance(tokens, torch.Tensor) or tokens.dtype != torch.int64 or tokens.ndim != 2 or tokens.shape[1] < 2:
-            raise ValueError("--tokens must contain a 2-D int64 tensor with sequence length >= 2")
-        if tokens.numel() == 0 or tokens.min() < 0 or tokens.max() >= vocab:
-            raise ValueError("Token IDs must be nonempty and within the model vocabulary")
-    else:
-        generator = torch.Generator().manual_seed(4321)
-        tokens = torch.randint(vocab, (args.steps * world * args.batch_size, args.seq_length), generator=generator)
-    dataset = TensorDataset(tokens)
-    sampler = DistributedSampler(dataset, num_replicas=world, rank=rank, shuffle=True, drop_last=True)
-    loader = DataLoader(dataset, batch_size=args.batch_size, sampler=sampler, drop_last=True)
-    if not len(loader):
-        raise ValueError("Dataset must provide at least one full batch per rank")
+    model = make_model(ns)
+    stream = batches(load_sequences(ns, model.config.vocab_size, ranks.world), ranks, ns.batch_size)
+    dp: Optional[SharedDataParallel] = None
+    if ranks.distributed:
+        dp = SharedDataParallel(chunk_numel=ns.chunk_numel, dtype=torch.bfloat16,
+                                exchange_slots=3 if ns.double_buffer else 2)
+    engine = SlideFormerOffloader(model, ranks.device, torch.bfloat16, double_buffer=ns.double_buffer,
+                                  enable_timing=False, enable_memory_stats=False, auto_backward_in_forward=False,
+                                  shared_dp=dp, update_chunk=ns.chunk_numel,
+                                  optimizer_kwargs={"lr": ns.lr, "weight_decay": 0.01, "fp32_optimizer_state": True})
+    engine.train()
+    before = [w.clone() for w in owned_master_weights(engine)] if ns.tiny else []
+    torch.manual_seed(1234 + ranks.rank)   # anything stochastic from here on differs per rank
 
-    dp = None
-    if distributed:
-        dp = SharedDataParallel(chunk_numel=args.chunk_numel, dtype=dtype, exchange_slots=3 if args.double_buffer else 2)
-    model = SlideFormerOffloader(
-        base_model, device=device, dtype=dtype, double_buffer=args.double_buffer, enable_timing=False,
-        enable_memory_stats=False, auto_backward_in_forward=False, shared_dp=dp,
-        optimizer_kwargs=dict(lr=args.lr, weight_decay=0.01, fp32_optimizer_state=True),
-        update_chunk=args.chunk_numel)
-    model.train()
-    initial = [layer._params_flat.clone() for layer in model.transformer_layers] if args.tiny else None
-    torch.manual_seed(1234 + rank)
-    completed, epoch = 0, 0
-    while completed < args.steps:
-        sampler.set_epoch(epoch)
-        for (input_ids,) in loader:
-            input_ids = input_ids.to(device)
-            loss = model(input_ids, labels=input_ids).loss
-            health = torch.isfinite(loss.detach()).to(torch.int64)
-            if distributed:
-                dist.all_reduce(health, op=dist.ReduceOp.MIN)
-            if not health.item():
-                raise RuntimeError("Nonfinite loss on at least one rank")
-            loss.backward()
-            model.wait_for_completion()
-            mean_loss = loss.detach().float()
-            if distributed:
-                dist.all_reduce(mean_loss)
-                mean_loss /= world
-            completed += 1
-            if rank == 0:
-                print(f"step={completed} global_loss={mean_loss.item():.6f} ranks={world}", flush=True)
-            if completed == args.steps:
-                break
-        epoch += 1
-    if args.tiny:
-        for before, layer in zip(initial, model.transformer_layers):
-            owned = layer._dp_state.end - layer._dp_state.start if dp is not None else layer.total_size
-            after, before = layer._params_flat[:owned], before[:owned]
-            if owned and (not torch.isfinite(after).all() or torch.equal(before, after)):
-                raise RuntimeError(f"Layer {layer.layer_idx} has invalid or unchanged weights")
-            steps_done = layer._dp_state.step if dp is not None else model.layer_optimizer.param_groups[layer.layer_idx]["step"]
-            if steps_done != completed:
-                raise RuntimeError("Incorrect optimizer step count")
-        print(f"rank={rank} tiny_weight_checks=passed", flush=True)
-    if args.save_model and rank == 0:
-        model.save_pretrained(args.save_model)
-    model.wait_for_completion()
+    done = 0
+    for done in range(1, ns.steps + 1):
+        ids = next(stream).to(ranks.device)
+        loss = engine(ids, labels=ids).loss
+        if not all_ranks_finite(loss, ranks):
+            raise RuntimeError("Nonfinite loss on at least one rank")
+        loss.backward()
+        engine.wait_for_completion()
+        shown = mean_over_ranks(loss, ranks)
+        if ranks.rank == 0:
+            print(f"step={done} global_loss={shown:.6f} ranks={ranks.world}", flush=True)
+
+    if ns.tiny:
+        self_check(engine, before, done, dp)
+        print(f"rank={ranks.rank} tiny_weight_checks=passed", flush=True)
+    if ns.save_model and ranks.rank == 0:
+        engine.save_pretrained(ns.save_model)
+    engine.wait_for_completion()
     if dp is not None:
         dp.barrier()
         dp.close()
-    print(f"rank={rank} completed={completed}", flush=True)
-    if distributed:
+    print(f"rank={ranks.rank} completed={done}", flush=True)
+    if ranks.distributed:
         dist.barrier()
         dist.destroy_process_group()
     return 0
