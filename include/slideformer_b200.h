@@ -145,7 +145,7 @@ int sf_dp_mean(const void* const* peer_g, int world, int g_dtype, float* mean, u
  * can fail, and even when it succeeds it stalls the device that the main thread is feeding
  * with kernels.  Such callers cannot allocate a staging buffer, and may not own one.
  *
- * Limit: n <= sf_static_scratch_max_elems() (4 Mi elements, a 16 MiB fp32 array that every GPU
+ * Limit: n <= SF_STATIC_SCRATCH_MAX_ELEMS (4 Mi elements, a 16 MiB fp32 array that every GPU
  * using the library holds until the process exits); larger n is rejected with SF_ERR_SIZE
  * before anything runs -- split the range into several calls.
  *
@@ -156,7 +156,7 @@ int sf_dp_mean(const void* const* peer_g, int world, int g_dtype, float* mean, u
  * it, but two calls that can run at the same time on the GPU (different streams, no ordering)
  * race on it: keep calls on one device ordered.  Other arguments as for sf_dp_mean and
  * sf_adam_update. */
-uint64_t sf_static_scratch_max_elems(void);
+#define SF_STATIC_SCRATCH_MAX_ELEMS (4u << 20)
 int sf_adam_update_dp_static(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
                              float weight_decay, int bias_correction, float* p,
                              const void* const* peer_g, int world, int g_dtype, float* m, float* v,

@@ -16,6 +16,7 @@ SF_ERR_NULL, SF_ERR_ALIGN, SF_ERR_SIZE, SF_ERR_UNKNOWN_ID, SF_ERR_CUDA, SF_ERR_D
 SF_GRAD_BF16, SF_GRAD_F32 = 0, 1
 SF_IPC_HANDLE_BYTES = 64
 SF_ABI_VERSION = 1
+SF_STATIC_SCRATCH_MAX_ELEMS = 4 << 20  # sf_adam_update_dp_static: largest n per call
 
 
 class SfAdamScalars(C.Structure):
@@ -48,7 +49,6 @@ SIGNATURES = {
     "sf_adam_step_sharded_push": (_i, [C.POINTER(SfAdamScalars), _vp, C.POINTER(_vp), C.POINTER(_vp), _i, _i, _vp, _vp,
                                        _u64, _u64, _vp]),
     "sf_dp_mean": (_i, [C.POINTER(_vp), _i, _i, _vp, _u64, _vp]),
-    "sf_static_scratch_max_elems": (_u64, []),
     "sf_adam_update_dp_static": (_i, [_i, _u64, _f, _f, _f, _f, _f, _i, _vp, C.POINTER(_vp), _i, _i, _vp, _vp, _vp,
                                       _u64, _vp]),
     "sf_adam_host_scratch_bytes": (C.c_size_t, [_u64, _i, _i]),

@@ -725,7 +725,7 @@ size_t round256(size_t x) { return (x + 255) & ~(size_t)255; }
 // Reserved in the library image itself: every GPU that loads the library carries these 16 MiB
 // until the process exits.  The name below is only a handle on the host; the device address
 // comes from cudaGetSymbolAddress, once per device, with that device current.
-constexpr uint64_t kStaticMeanMaxElems = (uint64_t)4 << 20;  // 4 Mi fp32 values = 16 MiB
+constexpr uint64_t kStaticMeanMaxElems = SF_STATIC_SCRATCH_MAX_ELEMS;  // 4 Mi fp32 values = 16 MiB
 static __device__ __align__(256) float g_static_mean[kStaticMeanMaxElems];
 
 std::mutex g_static_mu;
@@ -957,8 +957,6 @@ int sf_dp_mean(const void* const* peer_g, int world, int g_dtype, float* mean, u
     }
     return check_launch("dp_mean_kernel");
 }
-
-uint64_t sf_static_scratch_max_elems(void) { return kStaticMeanMaxElems; }
 
 int sf_adam_update_dp_static(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
                              float weight_decay, int bias_correction, float* p,

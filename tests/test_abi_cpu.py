@@ -116,7 +116,7 @@ def test_error_codes_without_gpu(lib):
     assert lib.sf_dp_mean(None, 2, 0, None, 16, None) == _lib.SF_ERR_NULL
     assert lib.sf_dp_mean(None, 2, 0, None, 0, None) == 0
     assert lib.sf_adam_update_dp_static(77, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, None, None, 2, 0, None, None, None,
-                                        lib.sf_static_scratch_max_elems() + 1, None) == _lib.SF_ERR_SIZE
+                                        _lib.SF_STATIC_SCRATCH_MAX_ELEMS + 1, None) == _lib.SF_ERR_SIZE
     assert lib.sf_adam_update_host(77, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, None, None, 0, 0, None, None, None,
                                    0, 24, 0, None, 0, None) == _lib.SF_ERR_ARG  # chunk not a multiple of 16
     assert lib.sf_adam_host_scratch_bytes(1024, 0, 1) == 2 * (3 * 4096 + 2048)

@@ -28,7 +28,7 @@ def test_static_scratch_matches_existing_entry_points_twice():
     from slideformer_b200 import _lib
     lib = _lib.load()
     world = 3
-    max_elems = lib.sf_static_scratch_max_elems()
+    max_elems = _lib.SF_STATIC_SCRATCH_MAX_ELEMS
     assert max_elems == 4 << 20
     stream = torch.cuda.current_stream().cuda_stream
     gen = torch.Generator().manual_seed(2024)
