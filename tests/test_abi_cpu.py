@@ -145,3 +145,40 @@ def test_layer_adam_host_rules_without_gpu():
     z = torch.zeros(4)
     with pytest.raises(RuntimeError, match="pinned"):
         opt.step_chunk(z, z.clone(), z.clone(), z.clone(), dict(opt.defaults, step=1))
+
+
+C_CLIENT = r"""
+#include <stdio.h>
+#include <string.h>
+#include "slideformer_b200.h"
+int main(void) {
+    SfAdamScalars s;
+    if (sf_abi_version() != SF_ABI_VERSION) return 2;
+    if (sf_adam_create(5, 1e-5f, 0.9f, 0.999f, 1e-8f, 0.01f, 1, 0) != SF_OK) return 3;
+    if (sf_adam_scalars(5, 1, 1e-5f, 0.9f, 0.999f, 1e-8f, 0.01f, 1, &s) != SF_OK) return 4;
+    if (sf_adam_scalars(6, 1, 1e-5f, 0.9f, 0.999f, 1e-8f, 0.01f, 1, &s) != SF_ERR_UNKNOWN_ID) return 5;
+    if (strstr(sf_last_error(), "6") == NULL) return 6;
+    if (sf_adam_update(5, 2, 1e-5f, 0.9f, 0.999f, 1e-8f, 0.01f, 1, NULL, NULL, SF_GRAD_BF16, NULL, NULL, NULL, 0, NULL) != SF_OK) return 7;
+    printf("%.9g %.9g %.9g %d %u\n", s.omb1, s.bc2, s.step_size, s.adamw_mode, (unsigned)SF_STATIC_SCRATCH_MAX_ELEMS);
+    return sf_adam_destroy(5);
+}
+"""
+
+
+def test_header_is_plain_c_and_links_from_c(tmp_path, oracle):
+    """The boundary is a C ABI: a C99 translation unit includes the header and links the library."""
+    import subprocess
+    from slideformer_b200 import _lib
+    _lib.load()
+    src = tmp_path / "client.c"
+    src.write_text(C_CLIENT)
+    exe = tmp_path / "client"
+    lib_dir = _lib.LIB_PATH.parent
+    subprocess.check_call(["/usr/bin/gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", f"-I{ROOT / 'include'}", str(src),
+                           "-o", str(exe), f"-L{lib_dir}", "-lslideformer_b200", f"-Wl,-rpath,{lib_dir}"])
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, (out.returncode, out.stdout, out.stderr)
+    omb1, bc2, step_size, adamw, max_elems = out.stdout.split()
+    c = oracle.OracleAdam(1e-5, 0.9, 0.999, 1e-8, 0.01, True).scalars(1, 1e-5, 0.9, 0.999, 1e-8, 0.01, True)
+    assert np.float32(float(omb1)) == np.float32(c.omb1) and np.float32(float(bc2)) == np.float32(c.bc2)
+    assert np.float32(float(step_size)) == np.float32(c.step_size) and adamw == "1" and int(max_elems) == 4 << 20
