@@ -89,7 +89,7 @@ class SlideFormerOffloader(nn.Module):
         if shared_dp is not None:
             if shared_dp.exchange_slots < n_units:
                 raise ValueError(f"shared_dp needs at least {n_units} exchange slots")
-            shared_dp._grow_exchange(-(-self.max_param_size // (16 * shared_dp.world_size)) * 16 * shared_dp.world_size)
+            shared_dp.reserve_exchange(self.max_param_size)
         self._grad_pool = None  # built after the layers registered (the exchange buffers may grow)
 
         self.weight_window = bool(weight_window)

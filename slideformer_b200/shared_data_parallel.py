@@ -157,6 +157,7 @@ class SharedDataParallel:
         # (peer-mapped stores); False: NCCL all-gather after the kernel.
         self.push_weights = bool(push_weights)
         self._weight_allocs = []            # (base, peers) of the IPC-visible bf16 layer buffers
+        self._views_out = False             # grad_buffer() views exist: the slots must not move any more
         self._cap = 0                       # elements per exchange slot
         self._base = None                   # local exchange allocation (raw pointer)
         self._peer_base: List[int] = []     # every rank's exchange base mapped here (own = local pointer)
@@ -202,10 +203,19 @@ class SharedDataParallel:
         self._peer_base = []
         self._base = None
 
+    def reserve_exchange(self, elems: int):
+        """Collective: make every exchange slot at least `elems` elements long.  Call it with the
+        largest layer size before handing out `grad_buffer()` views: growing the slots later
+        re-allocates them, which would leave such views dangling (and is refused)."""
+        self._grow_exchange(-(-int(elems) // (SHARD_ALIGN * self.world_size)) * SHARD_ALIGN * self.world_size)
+
     def _grow_exchange(self, elems: int):
         """Collective: (re)allocate the exchange slots for `elems` elements and map the peers'."""
         if elems <= self._cap:
             return
+        if self._views_out:
+            raise RuntimeError("a layer larger than the exchange slots was registered after grad_buffer() views "
+                               "were handed out; call reserve_exchange(largest_layer_numel) first")
         torch.cuda.synchronize(self.device)
         self.ctl.barrier()
         self._free_exchange()
@@ -224,6 +234,7 @@ class SharedDataParallel:
     def grad_buffer(self, slot: int = 0) -> torch.Tensor:
         """This rank's exchange slot (dtype = self.dtype, capacity >= the largest registered layer).
         Writing gradients straight into it saves the copy `reduce_chunk` would make."""
+        self._views_out = True
         return self._exchange[slot]
 
     def _peer_ptrs(self, slot: int, offset_elems: int):
