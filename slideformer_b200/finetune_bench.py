@@ -117,6 +117,29 @@ def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int,
     return line
 
 
+CSV_FIELDS = ["Model", "Sequence_Length", "Batch_Size", "Precision", "GPUs", "State_Device", "Activation_Offload",
+              "Activation_Checkpoint", "Avg_Time", "Avg_Tokens_Per_Second", "Avg_TFLOPS", "Max_CUDA_Memory_Allocated_MB"]
+
+
+def append_result_to_csv(path: str, line: dict) -> None:
+    """One row per run, in the spirit of the reference's results file (scripts/main_bench.py:65-95):
+    time per step, tokens/s, model TFLOPS and peak CUDA memory next to the run's settings."""
+    import csv
+    cfg = line["config"]
+    new_file = not os.path.isfile(path)
+    with open(path, "a", newline="") as fh:
+        w = csv.DictWriter(fh, fieldnames=CSV_FIELDS)
+        if new_file:
+            w.writeheader()
+        w.writerow({"Model": cfg["workload"].split()[0], "Sequence_Length": cfg["seq_len"],
+                    "Batch_Size": cfg["global_batch"] // line["n_gpus"], "Precision": line["dtype"],
+                    "GPUs": line["n_gpus"], "State_Device": cfg["state_device"],
+                    "Activation_Offload": cfg["activation_offload"], "Activation_Checkpoint": cfg["activation_checkpoint"],
+                    "Avg_Time": f"{line['ms_per_step'] / 1e3:.4f}", "Avg_Tokens_Per_Second": f"{line['value']:.1f}",
+                    "Avg_TFLOPS": f"{line['model_tflops']:.2f}",
+                    "Max_CUDA_Memory_Allocated_MB": f"{line['max_memory_gb'] * 1024:.1f}"})
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="gpt2-small")
@@ -134,6 +157,7 @@ def main(argv=None):
     ap.add_argument("--weight-window", action="store_true",
                     help="keep only bf16 slices resident and all-gather each layer into a window unit before it runs")
     ap.add_argument("--meta", action="store_true", help="build the model skeleton on the meta device (large models)")
+    ap.add_argument("--csv", metavar="FILE", help="also append the result as one CSV row")
     args = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -152,6 +176,8 @@ def main(argv=None):
                         args.weight_window, args.meta)
     if rank == 0:
         print(json.dumps(line))
+        if args.csv:
+            append_result_to_csv(args.csv, line)
     if dp is not None:
         dp.close()
         torch.distributed.destroy_process_group()

@@ -214,6 +214,31 @@ class SlideFormerOffloader(nn.Module):
                 out[u.layer_idx] = sum(a.elapsed_time(b) for a, b in spans) / len(spans)
         return out
 
+    def print_layer_stats(self, layer_idx=None, show_history: bool = False):
+        """Per-unit device time of the optimizer step under the reference's label "parameter update"
+        (offload_transformer.py:337-377).  show_history averages over all recorded steps, otherwise
+        the most recent step is shown; the transfer labels of the reference have no counterpart
+        because nothing is transferred."""
+        if not self.enable_timing:
+            return
+        torch.cuda.synchronize(self.device)
+        rows = []
+        for u in self.transformer_layers:
+            if layer_idx is not None and u.layer_idx != layer_idx:
+                continue
+            spans = u.timings["parameter_update"]
+            if spans:
+                used = spans if show_history else spans[-1:]
+                rows.append((u.layer_idx, sum(a.elapsed_time(b) for a, b in used) / len(used), len(used)))
+        if not rows:
+            return
+        print("\nHistorical Average Layer Statistics:" if show_history else "\nCurrent Step Layer Statistics:")
+        if layer_idx is None:
+            mean = sum(r[1] for r in rows) / len(rows)
+            print(f"  parameter update: {mean:.2f}ms (avg across {len(rows)} layers)")
+        else:
+            print(f"  parameter update: {rows[0][1]:.2f}ms (layer {layer_idx}, {rows[0][2]} calls)")
+
     def save_pretrained(self, output_dir):
         """Write HF-format weights cast to the compute dtype (offload_transformer.py:593-597).  The
         live parameters already are the bf16 weights, so the model saves itself."""

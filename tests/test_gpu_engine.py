@@ -221,3 +221,22 @@ def test_host_grad_stepper_matches_oracle(oracle):
     assert np.array_equal(_bits(pd), po.view(np.uint32))
     assert np.array_equal(_bits(md), mo.view(np.uint32)) and np.array_equal(_bits(vd), vo.view(np.uint32))
     assert np.array_equal(out_host.view(torch.int16).numpy().view(np.uint16), oo)
+
+
+def test_layer_stats_and_csv(tmp_path, capsys):
+    from slideformer_b200.finetune_bench import append_result_to_csv, run_finetune
+    line = run_finetune("llama-tiny", 2, 32, steps=2, warmup=1, dev=DEV)
+    assert line["value"] > 0 and line["gpu_launches"] == 2 * 5 and line["optimizer_ms_per_step"] > 0
+    append_result_to_csv(str(tmp_path / "r.csv"), line)
+    rows = (tmp_path / "r.csv").read_text().splitlines()
+    assert rows[0].startswith("Model,Sequence_Length") and rows[1].startswith("llama-tiny,32,2,bf16,1,hbm")
+    from slideformer_b200.model_compat import build_random_model
+    from slideformer_b200.offload_transformer import SlideFormerOffloader
+    eng = SlideFormerOffloader(build_random_model("llama-tiny", DEV), DEV, torch.bfloat16, enable_timing=True,
+                               enable_memory_stats=False, optimizer_kwargs=dict(HP))
+    ids = _ids(eng.config.vocab_size, 2, 16, 1)[0]
+    eng(ids, labels=ids)
+    eng.print_layer_stats()
+    eng.print_layer_stats(layer_idx=1, show_history=True)
+    out = capsys.readouterr().out
+    assert "Current Step Layer Statistics" in out and "parameter update" in out and "layer 1" in out
