@@ -214,6 +214,35 @@ class SlideFormerOffloader(nn.Module):
                 out[u.layer_idx] = sum(a.elapsed_time(b) for a, b in spans) / len(spans)
         return out
 
+    def _save_from_slices(self, output_dir):
+        """Window mode: every rank takes part in gathering each unit's bf16 slices; rank 0 collects
+        the full tensors in host memory and writes them.  Collective: call it on all ranks."""
+        dp = self.shared_dp
+        names = {id(p): n for n, p in self.base_model.named_parameters()}
+        state = {}
+        for unit in self.transformer_layers:
+            st = unit._dp_state
+            if st.shard == 0:
+                continue
+            full = torch.empty(st.shard * dp.world_size, dtype=self.dtype, device=self.device)
+            dp.gather_weights(unit.layer_idx, full)
+            if dp.rank == 0:
+                for local, p in unit._managed_named_params:
+                    off, shape, k = unit._param_maps[local]
+                    state[names[id(p)]] = full[off:off + k].view(shape).cpu()
+            del full
+        torch.cuda.synchronize(self.device)
+        if dp.rank == 0:
+            missing = [n for n, _ in self.base_model.named_parameters() if n not in state]
+            if missing:
+                raise RuntimeError(f"parameters without a unit: {missing[:5]}")
+            for n, b in self.base_model.named_buffers():   # persistent buffers, if a model has any
+                if n in self.base_model.state_dict(keep_vars=True) and not b.is_meta:
+                    state[n] = b.detach().cpu()
+            self.base_model.save_pretrained(output_dir, state_dict=state)
+        dp.barrier()
+        return output_dir
+
     def print_layer_stats(self, layer_idx=None, show_history: bool = False):
         """Per-unit device time of the optimizer step under the reference's label "parameter update"
         (offload_transformer.py:337-377).  show_history averages over all recorded steps, otherwise
@@ -244,7 +273,7 @@ class SlideFormerOffloader(nn.Module):
         live parameters already are the bf16 weights, so the model saves itself."""
         self.wait_for_completion()
         if self.weight_window:
-            raise NotImplementedError("saving from window-mode shards is not implemented")
+            return self._save_from_slices(output_dir)
         # every parameter is a view into its unit's flat buffer; hand the serializer independent copies
         state, seen = {}, {}
         for name, value in self.base_model.state_dict(keep_vars=True).items():

@@ -41,6 +41,19 @@ def _worker(rank, world, path, mode):
                 ids = torch.randint(0, eng.config.vocab_size, (2, 32), generator=torch.Generator().manual_seed(7)).to(dev)
                 losses.append(float(eng(ids, labels=ids).loss.detach()))
             assert all(np.isfinite(losses)) and losses[-1] < losses[0], losses   # same batch every step: loss falls
+            # save from the slices (collective) and reload on rank 0: same logits as the engine
+            import tempfile as _tf
+            ids = torch.randint(0, eng.config.vocab_size, (2, 16), generator=torch.Generator().manual_seed(8)).to(dev)
+            with torch.no_grad():
+                mine = eng(ids).logits.float()
+            out_dir = os.path.join(os.path.dirname(path), "saved")
+            eng.save_pretrained(out_dir)
+            if rank == 0:
+                from transformers import AutoModelForCausalLM
+                again = AutoModelForCausalLM.from_pretrained(out_dir, dtype=torch.bfloat16).to(dev)
+                with torch.no_grad():
+                    ref = again(input_ids=ids).logits.float()
+                assert torch.allclose(mine, ref, atol=2e-2, rtol=0), (mine - ref).abs().max().item()
             dp.barrier()
             dp.close()
             return
