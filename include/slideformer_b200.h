@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define SF_ABI_VERSION 1
+#define SF_ABI_VERSION 2
 
 typedef enum SfStatus {
     SF_OK = 0,
@@ -46,6 +46,19 @@ typedef enum SfStatus {
  * <float, BFloat16, float> and <float, float, float> of cpu_adam_impl.cpp:187-188. */
 typedef enum SfGradDtype { SF_GRAD_BF16 = 0, SF_GRAD_F32 = 1 } SfGradDtype;
 
+/* Gradient statistics gathered by the same pass that applies the update, so that a loss-health
+ * check (the reference tests isfinite(loss), multi_gpu/scripts/main_dp.py:102-105) or a
+ * gradient-norm figure costs no extra trip through HBM.  Lives in DEVICE memory, owned and
+ * zeroed by the caller; launches accumulate with atomics (one per CTA and lane), so sumsq is
+ * reproducible to rounding only.  In the data-parallel entry points g is the fp32 mean of the
+ * ranks' gradients and each rank accumulates the slice it owns. */
+#define SF_STATS_LANES 32
+typedef struct SfGradStats {
+    float sumsq[SF_STATS_LANES]; /* the sum of all lanes is sum(g*g) over the elements seen */
+    uint32_t nonfinite;          /* != 0 once any gradient element was Inf or NaN           */
+    uint32_t reserved[31];
+} SfGradStats;
+
 /* The per-call constants of the element loop, all binary32, computed on the host exactly as
  * Adam_Optimizer::Step_AVX derives them (cpu_adam.h:124-150). */
 typedef struct SfAdamScalars {
@@ -59,7 +72,15 @@ typedef struct SfAdamScalars {
     float w_decay;      /* -1 * _alpha * _weight_decay (AdamW)      */
     float weight_decay; /* _weight_decay (L2 mode adds wd*p to g)   */
     int32_t adamw_mode; /* 1 = decoupled decay, 0 = L2              */
+    /* Gradient-side additions (no counterpart in the reference's kernel; its training
+     * scripts do this work in separate passes).  With grad_scale == 1 and grad_stats == NULL
+     * the element loop is the reference's, bit for bit. */
+    float grad_scale;   /* g is multiplied by this (one rounded fp32 product) before the
+                           update; 1.0f = the gradient as it is                          */
+    SfGradStats* grad_stats; /* DEVICE pointer or NULL: the launch adds its share of
+                           sum(g*g) and its non-finite flag there (g before grad_scale)   */
 } SfAdamScalars;
+
 
 /* ---- optimizer objects: the scalar state machine --------------------------------------- */
 
@@ -79,6 +100,15 @@ int sf_adam_destroy(int id);
  * pow() depends on the call history. */
 int sf_adam_scalars(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
                     float weight_decay, int bias_correction, SfAdamScalars* out);
+
+/* Sets the gradient-side additions that every later sf_adam_scalars(id, ...) copies into its
+ * output (and therefore every sf_adam_update* call of this id applies): the multiplier and the
+ * device statistics block.  Defaults after sf_adam_create: 1.0f and NULL.  Typical use: the
+ * training loop computes grad_scale for the next step from the norm the last step measured
+ * (a delayed global-norm clip: a layer-wise optimizer updates layer k before layer k-1 has a
+ * gradient, so the current step's global norm does not exist yet) or uses it to undo a loss
+ * scale. */
+int sf_adam_set_grad_hooks(int id, float grad_scale, SfGradStats* grad_stats_dev);
 
 /* ---- the fused step, HBM-resident ------------------------------------------------------ */
 
@@ -112,8 +142,8 @@ int sf_adam_step(const SfAdamScalars* s, float* p, const void* g, int g_dtype, f
  *              elements of g_dtype; 1 <= world <= 16
  * The caller must order this launch after every rank has finished writing its gradient and
  * must keep the gradients unchanged until the launch completes (the kernel itself never
- * waits on another GPU).  All pointers must be 16-byte aligned and n a multiple of 8, except
- * that a scalar kernel handles any other case. */
+ * waits on another GPU).  The vector kernel runs when all pointers are 16-byte aligned; a
+ * grid-wide scalar kernel handles any other alignment. */
 int sf_adam_step_sharded(const SfAdamScalars* s, float* p, const void* const* peer_g, int world,
                          int g_dtype, float* m, float* v, uint16_t* p_bf16, uint64_t n,
                          uint64_t vec_n, void* stream);
@@ -125,7 +155,10 @@ int sf_adam_step_sharded(const SfAdamScalars* s, float* p, const void* const* pe
  * reference's "publish the weights to all ranks" step (one shared fp32 mapping read by every
  * rank, multi_gpu/shared_data_parallel.py:92-105) needs no separate collective.  The caller
  * orders the launch after all ranks wrote their gradients and must place a cross-rank stream
- * barrier after it before any rank reads the bf16 buffers.  The kernel never waits on a peer. */
+ * barrier after it before any rank reads the bf16 buffers.  The kernel never waits on a peer.
+ * The order of peer_out does not matter to the result; the order of peer_g is the order of the
+ * fp32 sum.  Buffers that are not 16-byte aligned are handled one element at a time, spread
+ * over the whole grid. */
 int sf_adam_step_sharded_push(const SfAdamScalars* s, float* p, const void* const* peer_g,
                                uint16_t* const* peer_out, int world, int g_dtype, float* m, float* v,
                                uint64_t n, uint64_t vec_n, void* stream);
@@ -208,6 +241,13 @@ uint64_t sf_launch_count(void);
  * setting.  Intended for benchmarking; the defaults (1, 0) are the measured best.  Not thread
  * safe. */
 int sf_set_tuning(int variant, int ctas_per_sm);
+
+/* Shape of the fused pull + push kernel (sf_adam_step_sharded_push).  vec: elements per thread,
+ * 4 (8-byte peer accesses) or 8 (16-byte peer accesses, bf16 gradients).  specialise_world:
+ * non-zero = use the kernels compiled for a world of 2, 4 or 8, in which every peer load of a
+ * thread is issued before the first add; 0 = always the runtime-world kernel.  Negative values
+ * keep the current setting; the defaults are (8, 1).  For benchmarking; not thread safe. */
+int sf_set_push_tuning(int vec, int specialise_world);
 
 /* cudaIpc plumbing for the sharded path: export a handle for a cudaMalloc'ed base pointer
  * and map a peer's handle into this process.  handle is SF_IPC_HANDLE_BYTES bytes. */

@@ -15,14 +15,23 @@ SF_OK = 0
 SF_ERR_NULL, SF_ERR_ALIGN, SF_ERR_SIZE, SF_ERR_UNKNOWN_ID, SF_ERR_CUDA, SF_ERR_DTYPE, SF_ERR_ARG = range(1, 8)
 SF_GRAD_BF16, SF_GRAD_F32 = 0, 1
 SF_IPC_HANDLE_BYTES = 64
-SF_ABI_VERSION = 1
+SF_ABI_VERSION = 2
 SF_STATIC_SCRATCH_MAX_ELEMS = 4 << 20  # sf_adam_update_dp_static: largest n per call
+
+
+SF_STATS_LANES = 32
+
+
+class SfGradStats(C.Structure):
+    """Device-resident block the kernels accumulate gradient statistics into (256 bytes)."""
+    _fields_ = [("sumsq", C.c_float * SF_STATS_LANES), ("nonfinite", C.c_uint32), ("reserved", C.c_uint32 * 31)]
 
 
 class SfAdamScalars(C.Structure):
     _fields_ = [("beta1", C.c_float), ("beta2", C.c_float), ("omb1", C.c_float), ("omb2", C.c_float),
                 ("bc2", C.c_float), ("eps", C.c_float), ("step_size", C.c_float),
-                ("w_decay", C.c_float), ("weight_decay", C.c_float), ("adamw_mode", C.c_int32)]
+                ("w_decay", C.c_float), ("weight_decay", C.c_float), ("adamw_mode", C.c_int32),
+                ("grad_scale", C.c_float), ("grad_stats", C.c_void_p)]
 
     def as_tuple(self):
         return tuple(getattr(self, k) for k, _ in self._fields_)
@@ -41,6 +50,7 @@ _f, _u64, _vp, _i = C.c_float, C.c_uint64, C.c_void_p, C.c_int
 SIGNATURES = {
     "sf_adam_create": (_i, [_i, _f, _f, _f, _f, _f, _i, _i]),
     "sf_adam_destroy": (_i, [_i]),
+    "sf_adam_set_grad_hooks": (_i, [_i, _f, _vp]),
     "sf_adam_scalars": (_i, [_i, _u64, _f, _f, _f, _f, _f, _i, C.POINTER(SfAdamScalars)]),
     "sf_adam_update": (_i, [_i, _u64, _f, _f, _f, _f, _f, _i, _vp, _vp, _i, _vp, _vp, _vp, _u64, _vp]),
     "sf_adam_step": (_i, [C.POINTER(SfAdamScalars), _vp, _vp, _i, _vp, _vp, _vp, _u64, _u64, _vp]),
@@ -58,6 +68,7 @@ SIGNATURES = {
     "sf_abi_version": (_i, []),
     "sf_launch_count": (_u64, []),
     "sf_set_tuning": (_i, [_i, _i]),
+    "sf_set_push_tuning": (_i, [_i, _i]),
     "sf_dev_alloc": (_i, [C.c_size_t, C.POINTER(_vp)]),
     "sf_dev_free": (_i, [_vp]),
     "sf_ipc_export": (_i, [_vp, _vp]),

@@ -12,6 +12,7 @@ import os
 import shutil
 import subprocess
 import sys
+import tempfile
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
@@ -51,18 +52,33 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not needs_build():
         return LIB
-    cmd = [nvcc_path(), *NVCC_FLAGS, f"-I{ROOT / 'include'}", f"-I{CSRC}"]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [str(s) for s in sources()] + ["-o", str(LIB)]
-    env = dict(os.environ)
+    nvcc = [nvcc_path()]
     # The host compiler must be the system g++; an exported CXX may point elsewhere.
-    cmd[1:1] = ["-ccbin", "/usr/bin/g++"] if Path("/usr/bin/g++").exists() else []
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True)
+    if Path("/usr/bin/g++").exists():
+        nvcc += ["-ccbin", "/usr/bin/g++"]
+    flags = [f for f in NVCC_FLAGS if f not in ("-shared",)]
+    common = [*flags, f"-I{ROOT / 'include'}", f"-I{CSRC}"] + (["-Xptxas", "-v"] if verbose else [])
+    env = dict(os.environ)
+    obj_dir = Path(tempfile.mkdtemp(prefix="sf_b200_obj_"))
+    # one nvcc process per translation unit, side by side
+    jobs = []
+    for src in sources():
+        obj = obj_dir / (src.stem + ".o")
+        cmd = [*nvcc, *common, "-c", str(src), "-o", str(obj)]
+        jobs.append((cmd, obj, subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    log = ""
+    for cmd, obj, proc in jobs:
+        out, _ = proc.communicate()
+        log += out
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + out)
+    link = [*nvcc, *flags, "-shared", *[str(o) for _, o, _ in jobs], "-o", str(LIB)]
+    res = subprocess.run(link, env=env, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        raise RuntimeError("link failed:\n" + " ".join(link) + "\n" + res.stdout + res.stderr)
+    shutil.rmtree(obj_dir, ignore_errors=True)
     if verbose:
-        print(res.stdout + res.stderr)
+        print(log + res.stdout + res.stderr)
     return LIB
 
 

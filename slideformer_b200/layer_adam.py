@@ -16,9 +16,11 @@ Placement rules
     through the GPU (`sf_adam_update_host`);
   * parameter in pageable host memory -> RuntimeError.  There is no CPU arithmetic here.
 
-Each call to the C ABI corresponds to exactly one `adam_update` call of the reference, so
-the host scalar state machine (running beta^t product vs pow(), cpu_adam.h:57-76) sees the
-same call history and the results stay bit-identical to the reference kernel.
+Each call to the C ABI on device tensors corresponds to exactly one `adam_update` call of the
+reference, so the host scalar state machine (running beta^t product vs pow(), cpu_adam.h:57-76)
+sees the same call history and the results stay bit-identical to the reference kernel.  A call
+on host-resident tensors is one reference call too, unless `step_chunk(..., host_chunk_calls=True)`
+asks for one reference call per streamed chunk (the reference engine's history).
 """
 from __future__ import annotations
 
@@ -86,6 +88,8 @@ class LayerAdam:
         self.bf16_flat: Dict[int, Optional[torch.Tensor]] = {}
         self.stream_chunk_numel = int(stream_chunk_numel)
         self._scratch: Dict[Any, torch.Tensor] = {}
+        self.grad_scale = 1.0
+        self._grad_stats: Optional[torch.Tensor] = None
 
     def __del__(self):
         lib = getattr(self, "_lib", None)
@@ -145,7 +149,8 @@ class LayerAdam:
     # ---- the one place that calls the C ABI ---------------------------------------------------
     def _adam_update(self, step, lr, beta1, beta2, eps, weight_decay, bias_correction,
                      p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
-                     bf16: Optional[torch.Tensor] = None):
+                     bf16: Optional[torch.Tensor] = None, host_chunk_calls: bool = False,
+                     host_chunk_numel: Optional[int] = None):
         _check_flat("params", p, torch.float32)
         _check_flat("grads", g)
         _check_flat("exp_avg", m, torch.float32)
@@ -179,7 +184,7 @@ class LayerAdam:
         if g_on_host and not g.is_pinned():
             raise RuntimeError("a host-resident gradient must be pinned")
         dev = bf16.device if bf16 is not None else (g.device if not g_on_host else torch.device("cuda", torch.cuda.current_device()))
-        chunk = max(16, min(self.stream_chunk_numel, (n + 15) // 16 * 16)) // 16 * 16
+        chunk = max(16, min(int(host_chunk_numel or self.stream_chunk_numel), (n + 15) // 16 * 16)) // 16 * 16
         with torch.cuda.device(dev):
             need = self._lib.sf_adam_host_scratch_bytes(chunk, gcode, int(g_on_host))
             key = (dev.index, need)
@@ -191,7 +196,7 @@ class LayerAdam:
             _lib.check(self._lib.sf_adam_update_host(
                 self.optimizer_id, int(step), lr, beta1, beta2, eps, weight_decay, int(bias_correction == 1),
                 p.data_ptr(), g.data_ptr(), gcode, int(g_on_host), m.data_ptr(), v.data_ptr(),
-                bf16.data_ptr() if bf16 is not None else None, n, chunk, 0,
+                bf16.data_ptr() if bf16 is not None else None, n, chunk, int(bool(host_chunk_calls)),
                 scratch.data_ptr(), need, stream))
 
     # ---- whole-layer steps (layer_adam.py:271-428) ----------------------------------------------
@@ -251,13 +256,23 @@ class LayerAdam:
         return group
 
     @torch.no_grad()
-    def step_chunk(self, param_flat, grad_flat, exp_avg_flat, exp_avg_sq_flat, param_group, bf16_flat=None):
+    def step_chunk(self, param_flat, grad_flat, exp_avg_flat, exp_avg_sq_flat, param_group, bf16_flat=None,
+                   host_chunk_calls: bool = False, host_chunk_numel: Optional[int] = None):
         """One update on caller-sliced flat tensors; `param_group` may be a plain dict with
         step, lr, betas, eps, weight_decay, bias_correction.  bf16_flat (an addition) receives
-        the rounded copy of the updated slice."""
+        the rounded copy of the updated slice.
+
+        For HOST-resident tensors the library cuts the range into chunks of `host_chunk_numel`
+        (default: the optimizer's stream_chunk_numel) and streams them through the GPU.  By
+        default that is ONE reference adam_update over the whole range (the scalar state machine
+        advances once).  host_chunk_calls=True makes it one reference call PER CHUNK, which is
+        what the reference engine does with its 32 Mi-element chunks
+        (transformer_layer.py:453-499): from the second chunk on beta^t comes from pow() instead
+        of the running product, which can differ in the last bit."""
         self._adam_update(param_group["step"], param_group["lr"], param_group["betas"][0], param_group["betas"][1],
                           param_group["eps"], param_group["weight_decay"], param_group["bias_correction"],
-                          param_flat, grad_flat, exp_avg_flat, exp_avg_sq_flat, bf16_flat)
+                          param_flat, grad_flat, exp_avg_flat, exp_avg_sq_flat, bf16_flat,
+                          host_chunk_calls=host_chunk_calls, host_chunk_numel=host_chunk_numel)
 
     @torch.no_grad()
     def end_chunk_step(self, layer_idx: int):
@@ -267,3 +282,43 @@ class LayerAdam:
         self.defaults["lr"] = new_lr
         for group in self.param_groups:
             group["lr"] = new_lr
+
+    # ---- gradient-side work folded into the same pass (no counterpart in the reference's kernel) ----
+    def set_grad_scale(self, scale: float):
+        """Multiply every incoming gradient by `scale` (one rounded fp32 product per element) inside
+        the update kernel: a clip factor derived from the norm the previous step measured, or the
+        inverse of a loss scale.  1.0 restores the reference's element loop bit for bit."""
+        self.grad_scale = float(scale)
+        self._push_grad_hooks()
+
+    def enable_grad_stats(self, device=None):
+        """Have every update launch add sum(g*g) and a non-finite flag of the gradients it consumed
+        (before `grad_scale`) to a 256-byte block on `device`; read it with `read_grad_stats()`.
+        The reference's scripts get the equivalent signal from separate passes
+        (isfinite(loss), multi_gpu/scripts/main_dp.py:102-105)."""
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._grad_stats = torch.zeros(64, dtype=torch.float32, device=dev)
+        self._push_grad_hooks()
+        return self._grad_stats
+
+    def disable_grad_stats(self):
+        self._grad_stats = None
+        self._push_grad_hooks()
+
+    def read_grad_stats(self, reset: bool = True) -> dict:
+        """Synchronises with the device.  Returns sum of squares, its square root and the non-finite
+        flag over every gradient element consumed since the last reset (this rank's slices only,
+        when the state is sharded)."""
+        if getattr(self, "_grad_stats", None) is None:
+            raise RuntimeError("call enable_grad_stats() first")
+        host = self._grad_stats.cpu()
+        if reset:
+            self._grad_stats.zero_()
+        sumsq = float(host[:_lib.SF_STATS_LANES].double().sum())
+        nonfinite = bool(host[_lib.SF_STATS_LANES:_lib.SF_STATS_LANES + 1].view(torch.int32).item() != 0)
+        return {"sumsq": sumsq, "norm": sumsq ** 0.5, "nonfinite": nonfinite}
+
+    def _push_grad_hooks(self):
+        stats = getattr(self, "_grad_stats", None)
+        _lib.check(self._lib.sf_adam_set_grad_hooks(self.optimizer_id, getattr(self, "grad_scale", 1.0),
+                                                    stats.data_ptr() if stats is not None else None))

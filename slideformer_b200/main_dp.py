@@ -188,8 +188,8 @@ def main(argv=None) -> int:
     if ns.tiny:
         self_check(engine, before, done, dp)
         print(f"rank={ranks.rank} tiny_weight_checks=passed", flush=True)
-    if ns.save_model and ranks.rank == 0:
-        engine.save_pretrained(ns.save_model)
+    if ns.save_model:
+        engine.save_pretrained(ns.save_model)   # collective: every rank calls it, rank 0 writes
     engine.wait_for_completion()
     if dp is not None:
         dp.barrier()

@@ -270,10 +270,22 @@ class SlideFormerOffloader(nn.Module):
 
     def save_pretrained(self, output_dir):
         """Write HF-format weights cast to the compute dtype (offload_transformer.py:593-597).  The
-        live parameters already are the bf16 weights, so the model saves itself."""
+        live parameters already are the bf16 weights, so the model saves itself.
+
+        With `shared_dp` this is COLLECTIVE, like the reference's data-parallel engine
+        (multi_gpu/offload_transformer.py:581-590): every rank calls it, the ranks meet at a
+        barrier, rank 0 alone serialises (every rank holds the full bf16 weights; in window mode
+        the slices are all-gathered first, which needs every rank), and a second barrier releases
+        them."""
         self.wait_for_completion()
         if self.weight_window:
+            self.shared_dp.barrier()
             return self._save_from_slices(output_dir)
+        if self.shared_dp is not None:
+            self.shared_dp.barrier()
+            if self.shared_dp.rank != 0:
+                self.shared_dp.barrier()
+                return output_dir
         # every parameter is a view into its unit's flat buffer; hand the serializer independent copies
         state, seen = {}, {}
         for name, value in self.base_model.state_dict(keep_vars=True).items():
@@ -281,4 +293,6 @@ class SlideFormerOffloader(nn.Module):
                 seen[id(value)] = value.detach().clone()
             state[name] = seen[id(value)]
         self.base_model.save_pretrained(output_dir, state_dict=state)
+        if self.shared_dp is not None:
+            self.shared_dp.barrier()
         return output_dir

@@ -243,6 +243,13 @@ class SharedDataParallel:
             arr[r] = self._peer_base[r] + (slot * self._cap + offset_elems) * self._esize
         return arr
 
+    def _push_ptrs(self, state, offset_elems: int):
+        """Every rank's bf16 layer buffer at `offset_elems`, starting with the next rank: the order
+        of the destinations does not change the result, and each rank starting at a different
+        peer keeps the ranks from storing to the same destination in the same order."""
+        w = self.world_size
+        return (C.c_void_p * w)(*[state.peer_bf16[(self.rank + 1 + j) % w] + 2 * offset_elems for j in range(w)])
+
     # ---- registration ----------------------------------------------------------------------
     def register_layer(self, layer_idx, numel, resident_bf16: bool = True) -> LayerState:
         if not self.ctl.all_same((layer_idx, int(numel))) or layer_idx in self.layers:
@@ -400,7 +407,7 @@ class SharedDataParallel:
                         self._gcode, state.exp_avg[lo:lo + k].data_ptr(), state.exp_avg_sq[lo:lo + k].data_ptr(),
                         state.bf16_shard[lo:lo + k].data_ptr(), k, vec_local, stream))
                 elif state.peer_bf16 is not None:
-                    outs = (C.c_void_p * self.world_size)(*[base + 2 * a for base in state.peer_bf16])
+                    outs = self._push_ptrs(state, a)
                     _lib.check(self._lib.sf_adam_step_sharded_push(
                         C.byref(sc), state.params[lo:lo + k].data_ptr(), self._peer_ptrs(slot, a), outs,
                         self.world_size, self._gcode, state.exp_avg[lo:lo + k].data_ptr(),
@@ -532,7 +539,7 @@ class ShardedLayerAdam:
             _lib.check(dp._lib.sf_adam_scalars(self.adam.optimizer_id, g["step"], g["lr"], g["betas"][0], g["betas"][1],
                                                g["eps"], g["weight_decay"], int(g["bias_correction"] == 1), C.byref(sc)))
             if k > 0 and st.peer_bf16 is not None:
-                outs = (C.c_void_p * dp.world_size)(*[base + 2 * st.start for base in st.peer_bf16])
+                outs = dp._push_ptrs(st, st.start)
                 _lib.check(dp._lib.sf_adam_step_sharded_push(
                     C.byref(sc), st.params.data_ptr(), dp._peer_ptrs(0, st.start), outs, dp.world_size, dp._gcode,
                     st.exp_avg.data_ptr(), st.exp_avg_sq.data_ptr(), k, k, torch.cuda.current_stream().cuda_stream))

@@ -322,8 +322,10 @@ class OffloadLayerWrapper(nn.Module):
                         ce = min(cs + self.update_chunk, n)
                         opt.step_chunk(self._params_flat[cs:ce], g[cs:ce], m[cs:ce], v[cs:ce], group, self._bf16_flat[cs:ce])
                 else:
-                    # host-resident state: one call, chunked and double-buffered inside the library
-                    opt.step_chunk(self._params_flat, g[:n], m, v, group, self._bf16_flat)
+                    # host-resident state: chunked and double-buffered inside the library, one
+                    # reference call per chunk like the reference's chunk consumer
+                    opt.step_chunk(self._params_flat, g[:n], m, v, group, self._bf16_flat,
+                                   host_chunk_calls=True, host_chunk_numel=self.update_chunk)
                 opt.end_chunk_step(self.layer_idx)
             if self.enable_timing:
                 t1.record(s)

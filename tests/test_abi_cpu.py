@@ -30,8 +30,9 @@ def test_header_symbols_are_exported_and_bound(lib):
 
 
 def test_struct_layout_matches_header():
-    from slideformer_b200._lib import SfAdamScalars
-    assert C.sizeof(SfAdamScalars) == 40
+    from slideformer_b200._lib import SfAdamScalars, SfGradStats
+    assert C.sizeof(SfAdamScalars) == 56 and SfAdamScalars.grad_scale.offset == 40 and SfAdamScalars.grad_stats.offset == 48
+    assert C.sizeof(SfGradStats) == 256 and SfGradStats.nonfinite.offset == 128
 
 
 def scal(lib, oid, *a):

@@ -164,6 +164,23 @@ def test_engine_modes_agree_bitwise(kw, oracle):
         assert st is not None and st.bytes_d2h > 0 and st.bytes_h2d > 0
 
 
+def test_host_state_keeps_the_reference_call_history_per_chunk(oracle):
+    """Units larger than the update chunk: the reference engine makes one adam_update per chunk
+    (transformer_layer.py:453-499), so from the second chunk on beta^t comes from pow().  The
+    host-resident mode must follow that history like the HBM-resident mode does: equal bits with
+    the same chunk size, over several steps, and both equal to the oracle called once per chunk
+    (checked inside _run_steps)."""
+    hbm, _ = _make("llama-tiny", update_chunk=4096)
+    host, _ = _make("llama-tiny", update_chunk=4096, state_device="host")
+    ids = _ids(hbm.config.vocab_size, 2, 32, 3, seed=4)
+    _run_steps(hbm, ids, oracle)
+    _run_steps(host, ids, oracle)
+    assert any(u.total_size > 2 * 4096 for u in host.transformer_layers)
+    for ub, uo in zip(hbm.transformer_layers, host.transformer_layers):
+        assert np.array_equal(_bits(ub._params_flat.to(DEV)), _bits(uo._params_flat.to(DEV))), ub.layer_idx
+        assert np.array_equal(_bits(ub._bf16_flat), _bits(uo._bf16_flat))
+
+
 def test_inference_forward_and_lr_update():
     eng, plain = _make("llama-tiny")
     ids = _ids(eng.config.vocab_size, 2, 16, 1)[0]
