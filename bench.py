@@ -37,11 +37,15 @@ HP = dict(lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
 WORKLOAD = "llama3.1-8b decoder layer, flat n=218112000, fp32 p/m/v + bf16 grad -> bf16 copy"
 METRIC = "LayerAdam Gparams/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised in
-# profiles/adam_vec4_kernel_llama8b_layer.md: at n = 218,112,000 reads are 3,053.7 MB
-# (14.00 B/param) and writes 2,993.5 MB, i.e. 14 B/param minus about 60 MB that is still dirty
-# in L2 when the kernel ends (the same shortfall, 53-57 MB, shows at n = 16,777,216: it does not
-# grow with n).  Scaled to a launch over `units` parameters.
+L2_BYTES = 126e6
+SWEEP_SIZES = (1_000_448, 16_000_000, N_LAYER, 1_000_000_512)   # "1M, 16M, 218M, 1B", multiples of 128 * 8
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of adam_vec4_kernel as ncu captured them
+# (a profiler cannot run inside a timed benchmark, so this is carried over, not re-measured): at
+# n = 218,112,000 reads are 3,053.7 MB (14.00 B/param) and writes 2,993.5 MB, i.e. 14 B/param
+# minus about 60 MB that is still dirty in L2 when the kernel ends (the same shortfall, 53-57 MB,
+# shows at n = 16,777,216: it does not grow with n).  Scaled to a launch over `units` parameters.
 def ncu_traffic_bytes(units: int) -> float:
     return 14.0 * units + max(14.0 * units - 60e6, 0.0)
 
@@ -230,6 +234,253 @@ def main_reference(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------
+# parity inside the benchmark: a few more steps, checked against the CPU oracle
+# ---------------------------------------------------------------------------------------------
+def _window_starts(a: int, b: int, width: int):
+    """Up to three [lo, hi) windows of [a, b): at the start, around the middle, at the end;
+    starts on multiples of 16 elements relative to the layer."""
+    k = b - a
+    if k <= 0:
+        return []
+    w = min(width, k)
+    lows = {a, a + ((k - w) // 2) // 16 * 16, max(a, (b - w) // 16 * 16)}
+    return sorted((lo, min(lo + w, b)) for lo in lows)
+
+
+def _rel_vec_n(n: int, lo: int, hi: int) -> int:
+    return min(max((n & ~15) - lo, 0), hi - lo)
+
+
+def parity_single(dev, p, m, v, out, grads, n, steps=3, width=1 << 16):
+    """N = 1: `steps` more updates with a fresh optimizer object (so the scalar call history is
+    known), three windows of p / m / v / bf16 compared with the oracle bit for bit."""
+    import numpy as np
+    import torch
+    from oracle import oracle as O
+    from slideformer_b200 import LayerAdam
+    hp = (HP["lr"], HP["betas"][0], HP["betas"][1], HP["eps"], HP["weight_decay"])
+    opt = LayerAdam(**HP)
+    orc = O.OracleAdam(*hp, True)
+    group = dict(opt.defaults, step=0)
+    wins = _window_starts(0, n, width)
+    cpu = [[t[lo:hi].cpu().numpy().copy() for t in (p, m, v)] + [np.zeros(hi - lo, np.uint16)] for lo, hi in wins]
+    for j in range(steps):
+        group["step"] += 1
+        g = grads[j % len(grads)]
+        opt.step_chunk(p, g, m, v, group, out)
+        c = orc.scalars(group["step"], *hp, True)
+        for (lo, hi), (pw, mw, vw, ow) in zip(wins, cpu):
+            gw = g[lo:hi].view(torch.int16).cpu().numpy().view(np.uint16)
+            O.apply_step(c, pw, gw, mw, vw, ow, vec_n=_rel_vec_n(n, lo, hi))
+    torch.cuda.synchronize()
+    elems = mism = 0
+    for (lo, hi), (pw, mw, vw, ow) in zip(wins, cpu):
+        for want, got in ((pw, p), (mw, m), (vw, v)):
+            mism += int((got[lo:hi].cpu().numpy().view(np.uint32) != want.view(np.uint32)).sum())
+            elems += hi - lo
+        mism += int((out[lo:hi].view(torch.int16).cpu().numpy().view(np.uint16) != ow).sum())
+        elems += hi - lo
+    return {"elements": elems, "mismatches": mism, "steps": steps, "windows": [list(w) for w in wins],
+            "what": "p, m, v and the bf16 copy after extra steps vs the CPU oracle, bit for bit"}
+
+
+def parity_sharded(sh, world, rank, dev, steps=3, width=1 << 16):
+    """N > 1: `steps` more sharded steps with a fresh optimizer object; for three windows of every
+    rank's owned slice the ranks' gradients are all-gathered, the oracle computes the fp32
+    rank-order mean and the reference update, and (a) the owner's p / m / v and (b) EVERY rank's
+    pushed bf16 copy of that window are compared bit for bit.  Totals are summed over ranks."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from oracle import oracle as O
+    from slideformer_b200 import LayerAdam
+    from slideformer_b200.shared_data_parallel import shard_range
+    hp = (HP["lr"], HP["betas"][0], HP["betas"][1], HP["eps"], HP["weight_decay"])
+    sh.adam = LayerAdam(**HP)
+    sh.group = dict(sh.adam.defaults, step=0)
+    orc = O.OracleAdam(*hp, True)
+    st, dp, n = sh.state, sh.dp, sh.numel
+    wins = {r: _window_starts(*shard_range(n, world, r), width) for r in range(world)}
+    a0 = st.start
+    cpu = [[t[lo - a0:hi - a0].cpu().numpy().copy() for t in (st.params, st.exp_avg, st.exp_avg_sq)]
+           + [np.zeros(hi - lo, np.uint16)] for lo, hi in wins[rank]]
+    for j in range(steps):
+        slot = j % dp.exchange_slots
+        sh.step(slot)
+        mine_rows = []
+        for r in range(world):
+            for lo, hi in wins[r]:
+                local = dp.grad_buffer(slot)[lo:hi].contiguous()
+                rows = [torch.empty_like(local) for _ in range(world)]
+                dist.all_gather(rows, local)
+                if r == rank:
+                    mine_rows.append(np.stack([x.view(torch.int16).cpu().numpy().view(np.uint16) for x in rows]))
+        c = orc.scalars(sh.group["step"], *hp, True)
+        for (lo, hi), rows, (pw, mw, vw, ow) in zip(wins[rank], mine_rows, cpu):
+            O.apply_step(c, pw, O.rank_mean(rows), mw, vw, ow, vec_n=_rel_vec_n(n, lo, hi))
+    torch.cuda.synchronize()
+    elems = mism = 0
+    for (lo, hi), (pw, mw, vw, ow) in zip(wins[rank], cpu):
+        for want, got in ((pw, st.params), (mw, st.exp_avg), (vw, st.exp_avg_sq)):
+            mism += int((got[lo - a0:hi - a0].cpu().numpy().view(np.uint32) != want.view(np.uint32)).sum())
+            elems += hi - lo
+    for r in range(world):                      # the pushed bf16 layer, on every rank
+        for wi, (lo, hi) in enumerate(wins[r]):
+            exp = (torch.from_numpy(cpu[wi][3].view(np.int16).copy()).to(dev) if r == rank
+                   else torch.empty(hi - lo, dtype=torch.int16, device=dev))
+            dist.broadcast(exp, src=r)
+            if st.bf16 is not None:
+                mism += int((st.bf16[lo:hi].view(torch.int16) != exp).sum().item())
+                elems += hi - lo
+    t = torch.tensor([elems, mism], dtype=torch.int64, device=dev)
+    dist.all_reduce(t)
+    return {"elements": int(t[0]), "mismatches": int(t[1]), "steps": steps, "windows_per_rank": len(wins[rank]),
+            "what": "owned p, m, v slices and every rank's pushed bf16 layer after extra sharded steps vs the CPU "
+                    "oracle fed with the all-gathered gradients (fp32 rank-order mean), bit for bit"}
+
+
+# ---------------------------------------------------------------------------------------------
+# the standalone Adam-step sweep (1M / 16M / 218M / 1B flat vectors)
+# ---------------------------------------------------------------------------------------------
+def sweep_single(dev, peak, main_entry):
+    """HBM-resident single-GPU step at each size.  Sizes whose working set fits in the L2 rotate
+    through enough independent (p, g, m, v, out) sets that every launch finds its data in HBM."""
+    import math
+    import torch
+    from slideformer_b200 import LayerAdam
+    rows = []
+    for ns in SWEEP_SIZES:
+        if ns == main_entry["n"]:
+            rows.append(main_entry)
+            continue
+        sets = max(1, min(64, math.ceil(4 * L2_BYTES / (BYTES_PER_PARAM * ns))))
+        gen = torch.Generator(device=dev).manual_seed(ns % 9973)
+        state = []
+        for _ in range(sets):
+            p = torch.empty(ns, device=dev).normal_(0, 0.02, generator=gen)
+            g = torch.empty(ns, device=dev).normal_(0, 1e-3, generator=gen).to(torch.bfloat16)
+            state.append((p, g, torch.zeros(ns, device=dev), torch.zeros(ns, device=dev),
+                          torch.empty(ns, device=dev, dtype=torch.bfloat16)))
+        opt = LayerAdam(**HP)
+        group = dict(opt.defaults, step=0)
+
+        def one(i):
+            p, g, m, v, o = state[i % sets]
+            group["step"] += 1
+            opt.step_chunk(p, g, m, v, group, o)
+        for i in range(max(3, sets)):
+            one(i)
+        torch.cuda.synchronize()
+        est_ms = max(BYTES_PER_PARAM * ns / (peak * 1e9) * 1e3, 0.004)
+        reps = int(min(max(100.0 / est_ms, 20), 2000))       # about 0.1 s of launches
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(reps):
+            one(i)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        gbs = BYTES_PER_PARAM * ns / (ms * 1e-3) / 1e9
+        rows.append({"n": ns, "ms": ms, "gparams_per_s": ns / (ms * 1e-3) / 1e9, "hbm_gbs": gbs, "frac": gbs / peak,
+                     "launches": reps, "state_sets": sets,
+                     "l2": "rotating sets exceed L2" if sets > 1 else "inputs exceed L2"})
+        del state
+        torch.cuda.empty_cache()
+    return rows
+
+
+def sweep_sharded(dev, world, mode, main_entry):
+    """The sharded step at each size: kernel alone (with its NVLink traffic) and the whole step
+    with its two cross-rank stream barriers.  Below a few million elements the step is bound by
+    the barriers' latency, not by bytes, and nothing is flushed between launches."""
+    import torch
+    from slideformer_b200.shared_data_parallel import ShardedLayerAdam
+    rows = []
+    for ns in SWEEP_SIZES:
+        if ns == main_entry["n"]:
+            rows.append(main_entry)
+            continue
+        sh = ShardedLayerAdam(numel=ns, device=dev, mode=mode, **HP)
+        gen = torch.Generator(device=dev).manual_seed(ns % 9973 + sh.dp.rank)
+        sh.params_shard.normal_(0, 0.02, generator=gen)
+        for k in range(3):
+            sh.grad_buffer(k).normal_(0, 1e-3, generator=gen)
+        for k in range(3):
+            sh.step(k)
+        kern_ms = sh.time_kernel_only(50)
+        cnt = [0]
+
+        def step():
+            cnt[0] += 1
+            sh.step(cnt[0] % 3)
+        step_ms = sh._timed(step, 50)
+        link = 2 * (world - 1) * sh.shard_numel * 2
+        rows.append({"n": ns, "ms": step_ms, "kernel_ms": kern_ms, "gparams_per_s": ns / (step_ms * 1e-3) / 1e9,
+                     "nvlink_gbs_per_direction": link / (kern_ms * 1e-3) / 1e9,
+                     "frac": link / (kern_ms * 1e-3) / 1e9 / 770.0, "launches": 50,
+                     "l2": "not flushed" if BYTES_PER_PARAM * ns / world < 4 * L2_BYTES else "inputs exceed L2"})
+        sh.close()
+        del sh
+        torch.cuda.empty_cache()
+    return rows
+
+
+def measure_nvlink(dp, dev, nbytes: int = 1 << 29, reps: int = 10) -> dict:
+    """What a bare copy kernel reaches between these GPUs (GB/s per direction per GPU): one GPU
+    storing to its neighbour with the rest idle, every GPU storing to its neighbour at once,
+    every GPU loading from its neighbour at once, and both at once (the traffic mix of the fused
+    pull + push kernel: reads and writes in both directions of every link)."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from slideformer_b200 import _lib
+    lib = _lib.load()
+    base, peers = dp._shared_alloc(2 * nbytes)
+    nxt = peers[(dp.rank + 1) % dp.world_size]
+    src = torch.empty(nbytes, dtype=torch.uint8, device=dev).zero_()
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    s2 = torch.cuda.Stream(dev)
+
+    def timed(push: bool, pull: bool, only_rank0: bool = False) -> float:
+        active = (dp.rank == 0) or not only_rank0
+        def once():
+            if not active:
+                return
+            cur = torch.cuda.current_stream(dev)
+            if push:
+                _lib.check(lib.sf_copy_bytes(nxt, src.data_ptr(), nbytes, cur.cuda_stream))
+            if pull:
+                st = s2 if push else cur
+                if push:
+                    s2.wait_stream(cur)
+                _lib.check(lib.sf_copy_bytes(dst.data_ptr(), nxt + nbytes, nbytes, st.cuda_stream))
+        once()
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            once()
+        torch.cuda.current_stream(dev).wait_stream(s2)
+        b.record()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([a.elapsed_time(b) / reps if active else 0.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return nbytes / (float(t.item()) * 1e-3) / 1e9
+
+    out = {"store_one_gpu_gbs": timed(True, False, only_rank0=True), "store_all_gpus_gbs": timed(True, False),
+           "load_all_gpus_gbs": timed(False, True), "store_and_load_all_gpus_gbs": timed(True, True),
+           "how": f"{nbytes >> 20} MiB per copy with the library's 16-byte copy kernel to / from the next rank's memory, "
+                  f"{reps} repetitions, CUDA events, max over ranks; reference figures: 770 GB/s measured peer copy, 900 nominal"}
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    dp._shared_free(base, peers)
+    return out
+
+
+
 def measure_pcie(dev, nbytes: int = 1 << 30, reps: int = 5) -> dict:
     """Plain pinned-memory copy bandwidth of this box: each direction alone and both at once.
     The denominators for the host-buffer paths (PCIe Gen5 x16: 63 GB/s per direction nominal)."""
@@ -267,7 +518,7 @@ def main_b200(args):
     import torch
     import torch.distributed as dist
     from slideformer_b200 import LayerAdam, _lib
-    from slideformer_b200.host_io import HostGradStepper
+    from slideformer_b200.host_io import HostGradStepper, pinned_empty
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -346,18 +597,23 @@ def main_b200(args):
     value = n / (ms_per_step * 1e-3) / 1e9
 
     # ---- per-launch duration of the dominant kernel (roofline numerator) -----------------------
-    R = min(max(K, 10), 50)
+    # at least 0.3 s of launches, so that the clocks are sampled well inside a loaded stretch
+    R = int(min(max(K, 50, 300.0 / max(ms_per_step, 1e-3)), 1000))
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(R)]
     if world == 1:
+        sampler.in_region = True
         for i in range(R):
             evs[i][0].record()
             one_step(i)
             evs[i][1].record()
         torch.cuda.synchronize()
+        sampler.in_region = False
         kern_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
     else:
+        sampler.in_region = True
         kern_ms = sh.time_kernel_only(R)
-        extra.update(sh.breakdown(R))
+        sampler.in_region = False
+        extra.update(sh.breakdown(50))
         # the same step seen from the data side: every rank contributed one full-layer gradient
         extra["dp_gradient_gparams_per_s"] = world * value
         barrier()
@@ -367,8 +623,8 @@ def main_b200(args):
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": ncu_traffic_bytes(units) if world == 1 else None,
                 "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs, burst copy)" if which == "measured" else "fallback 6650 GB/s",
-                "kernel": "adam_vec4_kernel", "kernel_ms": kern_ms, "bytes_per_launch": hbm_bytes_per_launch,
-                "frac_of_nominal_8000": achieved / 8000.0}
+                "kernel": "adam_vec4_kernel", "kernel_ms": kern_ms, "launches_timed": R,
+                "bytes_per_launch": hbm_bytes_per_launch, "frac_of_nominal_8000": achieved / 8000.0}
     if world > 1 and args.dp_mode == "fused":
         # The fused kernel is bound by NVLink, not HBM: per launch every GPU receives the (N-1)
         # peer gradient slices it pulls plus the (N-1) bf16 slices its peers push into it, and
@@ -377,7 +633,7 @@ def main_b200(args):
         link = link_bytes / (kern_ms * 1e-3) / 1e9
         roofline = {"bound": "nvlink", "achieved": link, "peak": 770.0, "unit": "GB/s", "frac": link / 770.0,
                     "traffic": None, "peak_source": "measured peer copy, 770 GB/s per direction per GPU",
-                    "kernel": "adam_vec4_push_kernel", "kernel_ms": kern_ms, "bytes_per_launch": link_bytes,
+                    "kernel": "adam_push_kernel", "kernel_ms": kern_ms, "launches_timed": R, "bytes_per_launch": link_bytes,
                     "note": "bytes received (= sent) per GPU per launch over NVLink",
                     "hbm": {"achieved": achieved, "peak": peak, "frac": achieved / peak,
                             "bytes_per_launch": hbm_bytes_per_launch}}
@@ -385,8 +641,10 @@ def main_b200(args):
     # ---- end to end through the public API with host buffers -----------------------------------
     e2e = None
     if world == 1:
-        g_host = [grads[k].cpu().pin_memory() for k in range(2)]
-        out_host = torch.empty(n, dtype=torch.bfloat16).pin_memory()
+        g_host = [pinned_empty(n, torch.bfloat16, dev) for _ in range(2)]
+        for k in range(2):
+            g_host[k].copy_(grads[k])
+        out_host = pinned_empty(n, torch.bfloat16, dev)
         stepper = HostGradStepper(opt, n, dev, chunk_numel=args.e2e_chunk, min_chunk_numel=args.e2e_min_chunk)
         E = max(3, min(K, 20))
         for i in range(3):
@@ -412,7 +670,7 @@ def main_b200(args):
         extra["pcie"] = measure_pcie(dev)
         # fully host-resident state (p, m, v and g in pinned host memory) streamed through the GPU
         if args.host_state:
-            ph, mh, vh = (torch.empty(n).pin_memory() for _ in range(3))
+            ph, mh, vh = (pinned_empty(n, torch.float32, dev) for _ in range(3))
             ph.copy_(p)
             mh.zero_()
             vh.zero_()
@@ -432,8 +690,31 @@ def main_b200(args):
                                        "path": "sf_adam_update_host: p, m, v, g in pinned host memory, double-buffered chunks"}
             del ph, mh, vh
     else:
-        e2e = sh.e2e(K)
+        e2e = sh.e2e(K, chunk_numel=args.e2e_chunk, min_chunk_numel=args.e2e_min_chunk)
     sampler.stop()
+
+    # ---- parity: a few more steps of the very objects that were timed, against the CPU oracle ----
+    if not args.no_parity:
+        parity = parity_single(dev, p, m, v, out, grads, n) if world == 1 else parity_sharded(sh, world, rank, dev)
+        if parity["mismatches"]:
+            raise SystemExit(f"parity check failed: {parity}")
+        extra["parity"] = parity
+
+    # ---- the size sweep (kernel alone at N = 1; kernel and whole step when sharded) --------------
+    if not args.no_sweep:
+        main_entry = {"n": n, "ms": ms_per_step, "kernel_ms": kern_ms, "gparams_per_s": value,
+                      "frac": roofline["frac"], "launches": K, "l2": "inputs exceed L2"}
+        if world == 1:
+            main_entry["hbm_gbs"] = BYTES_PER_PARAM * value
+            extra["sweep"] = sweep_single(dev, peak, main_entry)
+        else:
+            main_entry["nvlink_gbs_per_direction"] = roofline.get("achieved")
+            extra["sweep"] = sweep_sharded(dev, world, args.dp_mode, main_entry)
+    if world > 1 and not args.no_nvlink:
+        extra["nvlink"] = measure_nvlink(sh.dp, dev)
+        if roofline.get("bound") == "nvlink":
+            both = extra["nvlink"]["store_and_load_all_gpus_gbs"]
+            roofline["frac_of_measured_bidirectional_copy"] = roofline["achieved"] / both
 
     cpu_baseline = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
@@ -453,16 +734,22 @@ def main_b200(args):
             del sh
         gc.collect()
         torch.cuda.empty_cache()
-        jobs = [("gpt2-small", 20, 5, "hbm"), ("llama3.1-8b", 4, 2, "hbm")]
-        if args.finetune == "full" and world == 1:
-            jobs.append(("llama3.1-8b", 3, 1, "host"))
+        # (model, batch per GPU, seq, timed steps, warm-up, state placement, window mode + meta build)
+        jobs = [("gpt2-small", 8, 1024, 20, 5, "hbm", False), ("llama3.1-8b", 8, 1024, 4, 2, "hbm", False)]
+        if world == 1:
+            # the configuration as the benchmark list words it: host-pinned optimizer state
+            jobs.append(("llama3.1-8b", 8, 1024, 2, 1, "host", False))
+        if world == 8:
+            # Llama-3.1-70B: state sharded 1/8, bf16 weights kept as slices and gathered per layer
+            jobs.append(("llama3.1-70b", 4, 2048, 2, 1, "hbm", True))
         finetune = []
-        for name, fsteps, fwarm, state_dev in jobs:
+        for name, fbatch, fseq, fsteps, fwarm, state_dev, window in jobs:
             dp = None
             if world > 1:
                 from slideformer_b200.shared_data_parallel import SharedDataParallel
                 dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=2)
-            finetune.append(run_finetune(name, 8, 1024, fsteps, fwarm, dev, world, rank, dp, state_device=state_dev))
+            finetune.append(run_finetune(name, fbatch, fseq, fsteps, fwarm, dev, world, rank, dp, state_device=state_dev,
+                                         weight_window=window, meta=window))
             if dp is not None:
                 dp.close()
 
@@ -503,12 +790,15 @@ def main():
     ap.add_argument("--host-state", action="store_true", default=True)
     ap.add_argument("--no-host-state", dest="host_state", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of extra steps after the timed region")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the 1M / 16M / 218M / 1B size sweep")
+    ap.add_argument("--no-nvlink", action="store_true", help="N > 1: skip the bare-copy NVLink measurement")
     ap.add_argument("--variant", type=int, default=-1,
                     help="access pattern of the kernel (sf_set_tuning): 0 default caching, 1 streaming hints, 2 256-bit")
     ap.add_argument("--ctas-per-sm", type=int, default=-1, help="0 = one tile per CTA, k > 0 = persistent grid")
-    ap.add_argument("--finetune", default="all", choices=["none", "all", "full"],
-                    help="also report fine-tune tokens/s of GPT-2 small and Llama-3.1-8B through the engine "
-                         "(batch 8 x 1024 per GPU); 'full' adds the host-pinned-state mode at N=1")
+    ap.add_argument("--finetune", default="all", choices=["none", "all"],
+                    help="also report fine-tune tokens/s through the engine: GPT-2 small and Llama-3.1-8B (batch 8 x 1024 "
+                         "per GPU), Llama-3.1-8B with host-pinned state at N=1, Llama-3.1-70B (batch 4 x 2048 per GPU) at N=8")
     args = ap.parse_args()
     if args.impl == "reference":
         return main_reference(args)

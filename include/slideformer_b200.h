@@ -249,6 +249,12 @@ int sf_set_tuning(int variant, int ctas_per_sm);
  * keep the current setting; the defaults are (8, 1).  For benchmarking; not thread safe. */
 int sf_set_push_tuning(int vec, int specialise_world);
 
+/* A plain copy kernel (16-byte loads and stores; dst, src and bytes multiples of 16) on device
+ * pointers that may be local or peer-mapped.  It exists so that the NVLink traffic of the
+ * data-parallel kernels can be compared with what a bare copy reaches between the same GPUs,
+ * in one direction or with every GPU sending and receiving at once. */
+int sf_copy_bytes(void* dst, const void* src, size_t bytes, void* stream);
+
 /* cudaIpc plumbing for the sharded path: export a handle for a cudaMalloc'ed base pointer
  * and map a peer's handle into this process.  handle is SF_IPC_HANDLE_BYTES bytes. */
 #define SF_IPC_HANDLE_BYTES 64

@@ -585,6 +585,15 @@ const char* sf_last_error(void) { return t_err.c_str(); }
 int sf_abi_version(void) { return SF_ABI_VERSION; }
 uint64_t sf_launch_count(void) { return g_launches.load(); }
 
+int sf_copy_bytes(void* dst, const void* src, size_t bytes, void* stream)
+{
+    if (bytes == 0) return SF_OK;
+    if (!dst || !src) return fail(SF_ERR_NULL, "dst and src must be non-NULL");
+    if (!aligned(dst, 16) || !aligned(src, 16) || (bytes & 15))
+        return fail(SF_ERR_ALIGN, "dst, src and bytes must be multiples of 16");
+    return launch_copy16(dst, src, bytes / 16, (cudaStream_t)stream);
+}
+
 int sf_set_push_tuning(int vec, int specialise_world)
 {
     if (vec >= 0 && vec != 4 && vec != 8) return fail(SF_ERR_ARG, "vec must be 4 or 8 (or negative to keep the setting)");

@@ -164,6 +164,15 @@ int launch_push(const StepCtx& x, float* p, const void* const* peer_g, uint16_t*
     return push_any<float, 0, 4>(x, p, peer_g, peer_out, world, m, v, n, vec_n, a16, st);
 }
 
+int launch_copy16(void* dst, const void* src, uint64_t n16, cudaStream_t st)
+{
+    DevInfo di;
+    if (int rc = device_info(&di)) return rc;
+    const int grid = grid_for((n16 + 255) / 256, di.sms, 8);
+    copy16_kernel<<<grid, 256, 0, st>>>((uint4*)dst, (const uint4*)src, n16);
+    return check_launch("copy16_kernel");
+}
+
 int launch_mean(const void* const* peer_g, int world, int g_dtype, float* mean, uint64_t n, bool a16,
                 cudaStream_t st)
 {

@@ -607,4 +607,13 @@ dp_mean_kernel(GS gs, float* __restrict__ mean, uint64_t nvec, uint64_t n)
     for (uint64_t i = nvec + gtid; i < n; i += nthreads) mean[i] = gs.load1(i);
 }
 
+// Plain copy with 16-byte accesses (any 16-byte aligned pointers, local or peer-mapped): the
+// yardstick the data-parallel kernels' link traffic is compared with.
+static __global__ void __launch_bounds__(256)
+copy16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, uint64_t n16)
+{
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) dst[i] = src[i];
+}
+
 }  // namespace sfk

@@ -14,6 +14,7 @@ from typing import Optional
 import torch
 
 from .layer_adam import LayerAdam
+from .numa import numa_local, pinned_empty  # noqa: F401  (re-exported: host buffers belong on the GPU's NUMA node)
 
 
 def chunk_schedule(numel: int, chunk: int, min_chunk: int):

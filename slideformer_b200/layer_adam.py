@@ -111,6 +111,7 @@ class LayerAdam:
         rounded copy of the updated weights in the same kernel launch.
         """
         params = list(params)
+        bf16_params = list(bf16_params) if bf16_params is not None else None
         if not params:
             return -1
         for p in params:
@@ -125,11 +126,20 @@ class LayerAdam:
         elif dev.type == "cpu":
             if not all(p.is_pinned() for p in params):
                 raise RuntimeError("host-resident parameters must be in pinned memory; there is no CPU update path")
-            kw = dict(device="cpu", pin_memory=True)
+            kw = None
         else:
             raise RuntimeError(f"unsupported device type: {dev.type}")
-        self.exp_avg_flat[layer_idx] = torch.zeros(layer_numel, dtype=torch.float32, **kw)
-        self.exp_avg_sq_flat[layer_idx] = torch.zeros(layer_numel, dtype=torch.float32, **kw)
+        if kw is not None:
+            self.exp_avg_flat[layer_idx] = torch.zeros(layer_numel, dtype=torch.float32, **kw)
+            self.exp_avg_sq_flat[layer_idx] = torch.zeros(layer_numel, dtype=torch.float32, **kw)
+        else:
+            # pinned moments next to the GPU that will stream them (the device of the bf16 outputs,
+            # else the current device)
+            from .numa import pinned_empty
+            near = next((b.device for b in (bf16_params or []) if b is not None), None) if bf16_params is not None else None
+            near = near if near is not None else (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu")
+            self.exp_avg_flat[layer_idx] = pinned_empty(layer_numel, torch.float32, near).zero_()
+            self.exp_avg_sq_flat[layer_idx] = pinned_empty(layer_numel, torch.float32, near).zero_()
         bf16_list = list(bf16_params) if bf16_params is not None else [None] * len(params)
         if len(bf16_list) != len(params):
             raise ValueError("bf16_params must have one entry per parameter")

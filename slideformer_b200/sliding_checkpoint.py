@@ -19,6 +19,8 @@ from typing import List, Optional
 import torch
 from torch.autograd.graph import saved_tensors_hooks
 
+from .numa import pinned_empty
+
 
 class ActivationStore:
     """Pinned host tensors for every decoder layer plus the 2-deep device prefetch pool.
@@ -28,7 +30,8 @@ class ActivationStore:
     def __init__(self, num_layers: int, shape, dtype, device, pool_size: int = 2):
         self.device = torch.device(device)
         self.shape = tuple(shape)
-        self.host: List[torch.Tensor] = [torch.empty(self.shape, dtype=dtype).pin_memory() for _ in range(num_layers)]
+        numel = torch.Size(self.shape).numel()
+        self.host: List[torch.Tensor] = [pinned_empty(numel, dtype, device).view(self.shape) for _ in range(num_layers)]
         self.pool = [torch.empty(self.shape, dtype=dtype, device=self.device) for _ in range(pool_size)]
         self.pool_idx = 0
         self.stream = torch.cuda.Stream(device=self.device)

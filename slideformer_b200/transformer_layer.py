@@ -32,6 +32,7 @@ import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from .model_compat import TextModelParts, call_decoder_layer
+from .numa import pinned_empty
 from .sliding_checkpoint import SlidingCheckpoint
 
 # Optimizer chunk, in elements: the reference's D2H chunk (transformer_layer.py:26-27).
@@ -161,7 +162,7 @@ class OffloadLayerWrapper(nn.Module):
             if state_device == "hbm":
                 self._params_flat = torch.empty(n, dtype=torch.float32, device=device)
             else:
-                self._params_flat = torch.empty(n, dtype=torch.float32).pin_memory()
+                self._params_flat = pinned_empty(n, torch.float32, device)
             self._bf16_flat = torch.empty(n, dtype=dtype, device=device)
 
         self._param_maps = OrderedDict()

@@ -145,6 +145,40 @@ def _worker(rank, world, path, scenario):
             assert np.allclose(got, ref1[dp2_state.start:dp2_state.end], rtol=0, atol=2.5e-5)  # |step| <= lr, sign may flip on tiny means
             dp.barrier()
             dp.close()
+        elif scenario == "host_stepper":
+            # gradients in pinned host memory on every rank, bf16 slices back to host, pieces pipelined
+            from slideformer_b200.shared_data_parallel import ShardedHostStepper, ShardedLayerAdam
+            n = 300_000 + 37
+            hp = (1e-5, 0.9, 0.999, 1e-8, 0.01)
+            sh = ShardedLayerAdam(numel=n, device=dev, mode="fused", lr=hp[0], betas=hp[1:3], eps=hp[3], weight_decay=hp[4])
+            gen = torch.Generator().manual_seed(11)
+            p0 = torch.randn(n, generator=gen) * 0.02
+            sh.dp.load_full_params(0, p0.to(dev))
+            stepper = ShardedHostStepper(sh, chunk_numel=65536, min_chunk_numel=16384)
+            assert len(stepper.chunks) > 4
+            orc = O.OracleAdam(*hp, True)
+            p, m, v, o = p0.numpy().copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.uint16)
+            st = sh.state
+            k = st.end - st.start
+            out_host = torch.zeros(max(k, 1), dtype=torch.bfloat16).pin_memory()
+            for step in (1, 2, 3, 4):
+                rows = torch.stack([(torch.randn(n, generator=gen) * 1e-3).to(torch.bfloat16) for _ in range(world)])
+                g_host = rows[rank].clone().pin_memory()
+                stepper.step(g_host, out_host, join=(step % 2 == 0))   # odd steps overlap with the next one
+                mean = O.rank_mean(_np_rows(rows))
+                for a, b in stepper.chunks:                              # one reference call per piece
+                    orc.adam_update(step, *hp, True, p[a:b], mean[a:b], m[a:b], v[a:b], o[a:b])
+                if step % 2 == 1:
+                    torch.cuda.synchronize()   # g_host of this step is dropped next: let its uploads finish
+            stepper.join()
+            torch.cuda.synchronize()
+            assert np.array_equal(_bits(st.params[:k]), p[st.start:st.end].view(np.uint32))
+            assert np.array_equal(_bits(st.exp_avg[:k]), m[st.start:st.end].view(np.uint32))
+            assert np.array_equal(_bits(st.exp_avg_sq[:k]), v[st.start:st.end].view(np.uint32))
+            assert np.array_equal(out_host[:k].view(torch.int16).numpy().view(np.uint16), o[st.start:st.end])
+            assert np.array_equal(st.bf16[:n].view(torch.int16).cpu().numpy().view(np.uint16), o)
+            sh.dp.barrier()
+            sh.close()
         elif scenario == "error":
             dp = SharedDataParallel(chunk_numel=64, dtype=torch.bfloat16, timeout_seconds=60)
             dp.register_layer(0, 64)
@@ -199,6 +233,12 @@ def test_reference_dp_sequence_sharded(world, scenario):
 def test_medium_layer_fused_and_nccl(world, scenario):
     _need(world)
     _run(world, scenario)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_host_stepper(world):
+    _need(world)
+    _run(world, "host_stepper")
 
 
 def test_host_failure_reaches_every_rank():
