@@ -327,11 +327,12 @@ def parity_sharded(sh, world, rank, dev, steps=3, width=1 << 16):
             elems += hi - lo
     for r in range(world):                      # the pushed bf16 layer, on every rank
         for wi, (lo, hi) in enumerate(wins[r]):
-            exp = (torch.from_numpy(cpu[wi][3].view(np.int16).copy()).to(dev) if r == rank
-                   else torch.empty(hi - lo, dtype=torch.int16, device=dev))
+            exp = (torch.from_numpy(cpu[wi][3].astype(np.int32)).to(dev) if r == rank
+                   else torch.empty(hi - lo, dtype=torch.int32, device=dev))
             dist.broadcast(exp, src=r)
             if st.bf16 is not None:
-                mism += int((st.bf16[lo:hi].view(torch.int16) != exp).sum().item())
+                got = st.bf16[lo:hi].view(torch.int16).to(torch.int32) & 0xFFFF
+                mism += int((got != exp).sum().item())
                 elems += hi - lo
     t = torch.tensor([elems, mism], dtype=torch.int64, device=dev)
     dist.all_reduce(t)
@@ -382,9 +383,34 @@ def sweep_single(dev, peak, main_entry):
         torch.cuda.synchronize()
         ms = a.elapsed_time(b) / reps
         gbs = BYTES_PER_PARAM * ns / (ms * 1e-3) / 1e9
-        rows.append({"n": ns, "ms": ms, "gparams_per_s": ns / (ms * 1e-3) / 1e9, "hbm_gbs": gbs, "frac": gbs / peak,
-                     "launches": reps, "state_sets": sets,
-                     "l2": "rotating sets exceed L2" if sets > 1 else "inputs exceed L2"})
+        row = {"n": ns, "ms": ms, "gparams_per_s": ns / (ms * 1e-3) / 1e9, "hbm_gbs": gbs, "frac": gbs / peak,
+               "launches": reps, "state_sets": sets,
+               "l2": "rotating sets exceed L2" if sets > 1 else "inputs exceed L2"}
+        if est_ms < 0.1:
+            # a launch this short is bound by the host's launch rate; the same launches replayed from
+            # a CUDA graph show what the GPU itself needs per launch
+            try:
+                graph = torch.cuda.CUDAGraph()
+                per_graph = max(sets, 16)
+                with torch.cuda.graph(graph):
+                    for i in range(per_graph):
+                        one(i)
+                graph.replay()
+                torch.cuda.synchronize()
+                greps = max(3, reps // per_graph)
+                a.record()
+                for _ in range(greps):
+                    graph.replay()
+                b.record()
+                torch.cuda.synchronize()
+                gms = a.elapsed_time(b) / (greps * per_graph)
+                row.update({"graph_ms": gms, "graph_hbm_gbs": BYTES_PER_PARAM * ns / (gms * 1e-3) / 1e9,
+                            "graph_frac": BYTES_PER_PARAM * ns / (gms * 1e-3) / 1e9 / peak})
+                del graph
+            except Exception as exc:   # report, do not fail the benchmark over an optional figure
+                row["graph_ms"] = None
+                row["graph_note"] = repr(exc)[:200]
+        rows.append(row)
         del state
         torch.cuda.empty_cache()
     return rows
@@ -468,7 +494,10 @@ def measure_nvlink(dp, dev, nbytes: int = 1 << 29, reps: int = 10) -> dict:
         torch.cuda.synchronize(dev)
         t = torch.tensor([a.elapsed_time(b) / reps if active else 0.0], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return nbytes / (float(t.item()) * 1e-3) / 1e9
+        # bytes that crossed each direction of a GPU's links: its stores leave it, its loads enter
+        # it, and with every GPU doing both each direction carries one copy of each kind
+        per_direction = nbytes * (2 if (push and pull) else 1)
+        return per_direction / (float(t.item()) * 1e-3) / 1e9
 
     out = {"store_one_gpu_gbs": timed(True, False, only_rank0=True), "store_all_gpus_gbs": timed(True, False),
            "load_all_gpus_gbs": timed(False, True), "store_and_load_all_gpus_gbs": timed(True, True),
