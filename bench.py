@@ -452,6 +452,77 @@ def sweep_sharded(dev, world, mode, main_entry):
     return rows
 
 
+def fast_mode_nvls(sh, dev, world, n, reps=50):
+    """The NVLS variant beside the exact one: same layer, gradients reduced and weights
+    replicated inside the NVSwitch.  Reports its step time and how far three steps drift from
+    the exact kernel started from the same state and gradients."""
+    import torch
+    import torch.distributed as dist
+    from slideformer_b200 import LayerAdam
+    from slideformer_b200.shared_data_parallel import ShardedLayerAdam
+    try:
+        from torch._C._distributed_c10d import _SymmetricMemory
+        ok = bool(_SymmetricMemory.has_multicast_support(torch._C._autograd.DeviceType.CUDA, dev.index))
+    except Exception:
+        ok = False
+    flags = [None] * world
+    dist.all_gather_object(flags, ok)
+    if not all(flags):
+        return {"mode": "nvls", "unavailable": "the driver reports no NVLink multicast support on at least one GPU"}
+    try:
+        fast = ShardedLayerAdam(numel=n, device=dev, mode="nvls", **HP)
+    except Exception as exc:
+        return {"mode": "nvls", "unavailable": repr(exc)[:300]}
+    ex_st, fa_st = sh.state, fast.state
+    k = ex_st.end - ex_st.start
+    for slot in range(3):
+        fast.grad_buffer(slot).copy_(sh.grad_buffer(slot))
+    # timing first (state drifts, which does not matter for time)
+    fa_st.params.copy_(ex_st.params)
+    for slot in range(3):
+        fast.step(slot)
+    kern_ms = fast.time_kernel_only(reps)
+    cnt = [0]
+
+    def step():
+        cnt[0] += 1
+        fast.step(cnt[0] % 3)
+    step_ms = fast._timed(step, reps)
+    # accuracy: both modes from one state, three steps, fresh optimizer objects
+    start = ex_st.params.clone()
+    for obj, st in ((sh, ex_st), (fast, fa_st)):
+        st.params.copy_(start)
+        st.exp_avg.zero_()
+        st.exp_avg_sq.zero_()
+        obj.adam = LayerAdam(**HP)
+        obj.group = dict(obj.adam.defaults, step=0)
+        for slot in range(3):
+            obj.step(slot)
+    torch.cuda.synchronize(dev)
+    dp_abs = (fa_st.params[:k] - ex_st.params[:k]).abs().max() if k else torch.zeros((), device=dev)
+    m_ref = ex_st.exp_avg[:k].abs().max().clamp(min=1e-30) if k else torch.ones((), device=dev)
+    m_err = (fa_st.exp_avg[:k] - ex_st.exp_avg[:k]).abs().max() / m_ref if k else torch.zeros((), device=dev)
+    same = (fa_st.params[:k].view(torch.int32) == ex_st.params[:k].view(torch.int32)).float().mean() if k else torch.ones((), device=dev)
+    bf_same = (fast.state.bf16[:n].view(torch.int16) == sh.state.bf16[:n].view(torch.int16)).float().mean()
+    t = torch.stack([dp_abs.float(), m_err.float()])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    u = torch.stack([same.float(), bf_same.float()])
+    dist.all_reduce(u, op=dist.ReduceOp.MIN)
+    received = 2 * fast.shard_numel * (world - 1) + 2 * fast.shard_numel   # pushed weights + reduced gradients
+    out = {"mode": "nvls", "exact": False, "parallelism": fast.describe(), "ms_per_step": step_ms, "kernel_ms": kern_ms,
+           "value": n / (step_ms * 1e-3) / 1e9, "unit": "Gparams/s",
+           "dp_gradient_gparams_per_s": world * n / (step_ms * 1e-3) / 1e9,
+           "nvlink_bytes_received_per_launch": received,
+           "nvlink_gbs_received": received / (kern_ms * 1e-3) / 1e9,
+           "accuracy_vs_exact": {"steps": 3, "max_abs_param_difference": float(t[0]),
+                                 "max_abs_param_difference_over_lr": float(t[0]) / HP["lr"],
+                                 "max_exp_avg_difference_over_max_exp_avg": float(t[1]),
+                                 "min_fraction_of_fp32_params_bit_identical": float(u[0]),
+                                 "min_fraction_of_bf16_weights_bit_identical": float(u[1])}}
+    fast.close()
+    return out
+
+
 def measure_nvlink(dp, dev, nbytes: int = 1 << 29, reps: int = 10) -> dict:
     """What a bare copy kernel reaches between these GPUs (GB/s per direction per GPU): one GPU
     storing to its neighbour with the rest idle, every GPU storing to its neighbour at once,
@@ -739,6 +810,8 @@ def main_b200(args):
         else:
             main_entry["nvlink_gbs_per_direction"] = roofline.get("achieved")
             extra["sweep"] = sweep_sharded(dev, world, args.dp_mode, main_entry)
+    if world > 1 and args.dp_mode == "fused" and not args.no_fast_mode:
+        extra["fast_mode"] = fast_mode_nvls(sh, dev, world, n)
     if world > 1 and not args.no_nvlink:
         extra["nvlink"] = measure_nvlink(sh.dp, dev)
         if roofline.get("bound") == "nvlink":
@@ -813,7 +886,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--n", type=int, default=N_LAYER, help="flat layer size (parity and sweep runs only)")
-    ap.add_argument("--dp-mode", default="fused", choices=["fused", "fused_ag", "nccl"])
+    ap.add_argument("--dp-mode", default="fused", choices=["fused", "fused_ag", "nccl", "nvls"])
     ap.add_argument("--e2e-chunk", type=int, default=16 * 1024 * 1024)
     ap.add_argument("--e2e-min-chunk", type=int, default=4 * 1024 * 1024)
     ap.add_argument("--host-state", action="store_true", default=True)
@@ -822,6 +895,8 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of extra steps after the timed region")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1M / 16M / 218M / 1B size sweep")
     ap.add_argument("--no-nvlink", action="store_true", help="N > 1: skip the bare-copy NVLink measurement")
+    ap.add_argument("--no-fast-mode", action="store_true",
+                    help="N > 1: skip the NVLS (in-switch reduction) variant that is reported beside the exact kernel")
     ap.add_argument("--variant", type=int, default=-1,
                     help="access pattern of the kernel (sf_set_tuning): 0 default caching, 1 streaming hints, 2 256-bit")
     ap.add_argument("--ctas-per-sm", type=int, default=-1, help="0 = one tile per CTA, k > 0 = persistent grid")

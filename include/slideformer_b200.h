@@ -163,6 +163,26 @@ int sf_adam_step_sharded_push(const SfAdamScalars* s, float* p, const void* cons
                                uint16_t* const* peer_out, int world, int g_dtype, float* m, float* v,
                                uint64_t n, uint64_t vec_n, void* stream);
 
+/* No counterpart in the reference: sf_adam_step_sharded_push with the exchange done inside the
+ * NVSwitch (NVLS).  mc_g / mc_out are MULTICAST device addresses (cuMulticast* objects bound to
+ * the same offset of every rank's bf16 gradient buffer / bf16 layer buffer) at this slice;
+ * peer_g / peer_out are the ordinary per-rank addresses of the same slice as in
+ * sf_adam_step_sharded_push.  For elements below the last multiple of 8 under vec_n the kernel
+ * issues one multimem.ld_reduce (the switch adds the ranks' bf16 gradients in fp32 and returns
+ * the sum rounded to bf16) and one multimem.st (the switch replicates the bf16 weights to every
+ * rank); the few remaining elements take the exact peer path.  Per launch a GPU then receives
+ * n * 2 * (world - 1) / world bytes of pushed weights plus n * 2 / world bytes of reduced gradients
+ * instead of twice the former, and sends about as much.
+ *
+ * NOT bit-exact: the switch's summation order is unspecified and its result is rounded to bf16
+ * before the division by world, so the mean differs from the reference's fp32 rank-order mean
+ * (multi_gpu/shared_data_parallel.py:130-133) by up to half a bf16 ulp of the sum, which is the
+ * accuracy of an NCCL bf16 reduce-scatter.  bf16 gradients only; gradient / bf16 addresses 16-byte
+ * and p, m, v 32-byte aligned.  Ordering rules as for sf_adam_step_sharded_push. */
+int sf_adam_step_sharded_nvls(const SfAdamScalars* s, float* p, const void* mc_g, uint16_t* mc_out,
+                               const void* const* peer_g, uint16_t* const* peer_out, int world, float* m,
+                               float* v, uint64_t n, uint64_t vec_n, void* stream);
+
 /* The gradient mean alone, for callers that keep the reference's update(params, mean, m, v)
  * callback (shared_data_parallel.py:130-135): mean[i] = (0 + g_0[i] + ... + g_{world-1}[i]) / world
  * in fp32, rank order.  mean is a local fp32[n] device buffer. */

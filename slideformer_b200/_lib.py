@@ -58,6 +58,8 @@ SIGNATURES = {
                                   _u64, _u64, _vp]),
     "sf_adam_step_sharded_push": (_i, [C.POINTER(SfAdamScalars), _vp, C.POINTER(_vp), C.POINTER(_vp), _i, _i, _vp, _vp,
                                        _u64, _u64, _vp]),
+    "sf_adam_step_sharded_nvls": (_i, [C.POINTER(SfAdamScalars), _vp, _vp, _vp, C.POINTER(_vp), C.POINTER(_vp), _i, _vp, _vp,
+                                       _u64, _u64, _vp]),
     "sf_dp_mean": (_i, [C.POINTER(_vp), _i, _i, _vp, _u64, _vp]),
     "sf_adam_update_dp_static": (_i, [_i, _u64, _f, _f, _f, _f, _f, _i, _vp, C.POINTER(_vp), _i, _i, _vp, _vp, _vp,
                                       _u64, _vp]),

@@ -461,6 +461,23 @@ int sf_adam_step_sharded_push(const SfAdamScalars* s, float* p, const void* cons
     return launch_push(x, p, peer_g, peer_out, world, g_dtype, m, v, n, vec_n, a16, (cudaStream_t)stream);
 }
 
+int sf_adam_step_sharded_nvls(const SfAdamScalars* s, float* p, const void* mc_g, uint16_t* mc_out,
+                               const void* const* peer_g, uint16_t* const* peer_out, int world, float* m,
+                               float* v, uint64_t n, uint64_t vec_n, void* stream)
+{
+    bool a16 = false;
+    if (int rc = check_peers(s, p, peer_g, peer_out, true, world, SF_GRAD_BF16, m, v, nullptr, n, &a16)) return rc;
+    if (n == 0) return SF_OK;
+    if (!mc_g || !mc_out) return fail(SF_ERR_NULL, "the multicast addresses must be non-NULL");
+    if (!a16 || !aligned(mc_g, 16) || !aligned(mc_out, 16) || !aligned(p, 32) || !aligned(m, 32) || !aligned(v, 32))
+        return fail(SF_ERR_ALIGN, "the multicast path needs 16-byte aligned gradient / bf16 addresses and 32-byte "
+                                  "aligned p, m, v; use sf_adam_step_sharded_push for other layouts");
+    if (vec_n > n) vec_n = n;
+    StepCtx x;
+    make_ctx(s, &x);
+    return launch_nvls(x, p, mc_g, mc_out, peer_g, peer_out, world, m, v, n, vec_n, (cudaStream_t)stream);
+}
+
 int sf_dp_mean(const void* const* peer_g, int world, int g_dtype, float* mean, uint64_t n, void* stream)
 {
     if (g_dtype != SF_GRAD_BF16 && g_dtype != SF_GRAD_F32)

@@ -164,6 +164,29 @@ int launch_push(const StepCtx& x, float* p, const void* const* peer_g, uint16_t*
     return push_any<float, 0, 4>(x, p, peer_g, peer_out, world, m, v, n, vec_n, a16, st);
 }
 
+int launch_nvls(const StepCtx& x, float* p, const void* mc_g, uint16_t* mc_out, const void* const* peer_g,
+                uint16_t* const* peer_out, int world, float* m, float* v, uint64_t n, uint64_t vec_n,
+                cudaStream_t st)
+{
+    DevInfo di;
+    if (int rc = device_info(&di)) return rc;
+    auto gs = make_peers<uint16_t, 0>(peer_g, world);
+    auto dst = make_dst<0>(peer_out, world);
+    const uint64_t body = vec_n < n ? vec_n : n;
+    const uint64_t nvec = body & ~(uint64_t)7;
+    uint64_t ctas = (nvec + 2047) / 2048;
+    const uint64_t rem_ctas = (n - nvec + 255) / 256;
+    const uint64_t rem_cap = (uint64_t)di.sms * 8;
+    if (ctas < (rem_ctas < rem_cap ? rem_ctas : rem_cap)) ctas = rem_ctas < rem_cap ? rem_ctas : rem_cap;
+    const int grid = grid_for(ctas, di.sms, 0);
+    return dispatch_mode_ex(x.mode, x.ex, [&](auto MODE, auto EX) -> int {
+        constexpr int M = decltype(MODE)::value;
+        constexpr bool E = decltype(EX)::value;
+        adam_nvls_kernel<M, E><<<grid, 256, 0, st>>>(x.c, p, (const uint16_t*)mc_g, m, v, mc_out, gs, dst, nvec, n, vec_n, x.stats);
+        return check_launch("adam_nvls_kernel");
+    });
+}
+
 int launch_copy16(void* dst, const void* src, uint64_t n16, cudaStream_t st)
 {
     DevInfo di;

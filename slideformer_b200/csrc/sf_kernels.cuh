@@ -591,6 +591,62 @@ adam_push_kernel(K c, float* __restrict__ p, GradPeers<ELT, W> gs, float* __rest
     if (EX) stat_flush<256>(acc, stats);
 }
 
+// The same step with the exchange done by the NVSwitch (NVLS): `mc_g` and `mc_out` are MULTICAST
+// addresses that alias the same offset of every rank's gradient buffer / bf16 layer buffer.
+//   multimem.ld_reduce  one 16-byte request returns the sum of all ranks' 8 bf16 gradients, added
+//                       inside the switch in fp32 and rounded once to bf16; only the reduced
+//                       16 bytes cross this GPU's ingress links instead of (world - 1) * 16;
+//   multimem.st         one 16-byte store is replicated by the switch into every rank's bf16
+//                       layer; it crosses this GPU's egress links once instead of world - 1 times.
+// The sum's order inside the switch is not specified and it is rounded to bf16 before the
+// division by world, so the gradient mean differs from the reference's fp32 rank-order mean by
+// up to half a bf16 ulp of the sum: this kernel is NOT bit-exact and is offered beside the exact
+// adam_push_kernel, never in its place.  Elements [nvec, n) take the exact peer path.
+// The kernel waits on nothing; the caller orders it between two cross-rank stream barriers.
+template <int MODE, bool EX>
+__global__ void __launch_bounds__(256, 3)
+adam_nvls_kernel(K c, float* __restrict__ p, const uint16_t* mc_g, float* __restrict__ m,
+                 float* __restrict__ v, uint16_t* mc_out, GradPeers<uint16_t, 0> gs, OutPush<0> dst,
+                 uint64_t nvec, uint64_t n, uint64_t vec_n, SfGradStats* stats)
+{
+    StatAcc acc{0.f, 0u};
+    const uint64_t i = ((uint64_t)blockIdx.x * 256 + threadIdx.x) * 8;
+    if (i < nvec) {
+        uint4 q;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                     : "l"(mc_g + i)
+                     : "memory");
+        f8 P = ld8(p + i), M = ld8(m + i), V = ld8(v + i);
+        float G[8];
+        G[0] = bf16_bits_to_f32(q.x & 0xffffu); G[1] = bf16_bits_to_f32(q.x >> 16);
+        G[2] = bf16_bits_to_f32(q.y & 0xffffu); G[3] = bf16_bits_to_f32(q.y >> 16);
+        G[4] = bf16_bits_to_f32(q.z & 0xffffu); G[5] = bf16_bits_to_f32(q.z >> 16);
+        G[6] = bf16_bits_to_f32(q.w & 0xffffu); G[7] = bf16_bits_to_f32(q.w >> 16);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            float g = __fdiv_rn(G[k], gs.fworld);
+            if (EX) g = grad_pre<EX>(c, g, acc);
+            adam_body<MODE>(c, P.x[k], g, M.x[k], V.x[k]);
+        }
+        st8(p + i, P);
+        st8(m + i, M);
+        st8(v + i, V);
+        uint4 o;
+        o.x = pack_bf16x2(P.x[0], P.x[1]);
+        o.y = pack_bf16x2(P.x[2], P.x[3]);
+        o.z = pack_bf16x2(P.x[4], P.x[5]);
+        o.w = pack_bf16x2(P.x[6], P.x[7]);
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_out + i), "r"(o.x),
+                     "r"(o.y), "r"(o.z), "r"(o.w)
+                     : "memory");
+    }
+    scalar_range<GradPeers<uint16_t, 0>, MODE, OutPush<0>, EX>(c, p, gs, m, v, dst, nvec, n, vec_n,
+                                                               (uint64_t)blockIdx.x * 256 + threadIdx.x,
+                                                               (uint64_t)gridDim.x * 256, acc);
+    if (EX) stat_flush<256>(acc, stats);
+}
+
 // fp32 rank-ordered mean of the peers' gradients, 4 elements per thread-iteration; elements
 // [nvec, n) one at a time, spread over the grid.
 template <typename GS>

@@ -77,6 +77,7 @@ class LayerState:
     end: int = 0
     bf16: Optional[torch.Tensor] = None  # full layer, bf16, padded to shard * world: all-gather target
     peer_bf16: Optional[list] = None     # base pointer of every rank's `bf16` (push mode only)
+    mc_bf16: int = 0                     # multicast address aliasing every rank's `bf16` (NVLS mode only)
     bf16_shard: Optional[torch.Tensor] = None  # window mode: only this rank's bf16 slice is kept; the full
                                                # layer is all-gathered into a window unit when it is needed
 
@@ -127,7 +128,7 @@ class SharedDataParallel:
     chunk order on every rank."""
 
     def __init__(self, chunk_numel=32 * 1024 * 1024, dtype=torch.bfloat16, shm_dir=None, timeout_seconds=120,
-                 *, device=None, exchange_slots: int = 2, push_weights: bool = True):
+                 *, device=None, exchange_slots: int = 2, push_weights: bool = True, nvls: bool = False):
         if not dist.is_initialized():
             raise RuntimeError("Initialize torch.distributed before SharedDataParallel")
         if chunk_numel < 1:
@@ -150,12 +151,22 @@ class SharedDataParallel:
         self._lib = _lib.load()
         self._gcode = _lib.SF_GRAD_BF16 if dtype == torch.bfloat16 else _lib.SF_GRAD_F32
         self._esize = 2 if dtype == torch.bfloat16 else 4
-        if not self.ctl.all_same((socket.gethostname(), self.chunk_numel, str(dtype), exchange_slots, bool(push_weights))):
+        if nvls and (dtype != torch.bfloat16 or not push_weights):
+            raise ValueError("nvls needs bfloat16 gradients and push_weights")
+        if not self.ctl.all_same((socket.gethostname(), self.chunk_numel, str(dtype), exchange_slots, bool(push_weights),
+                                  bool(nvls))):
             raise ValueError("SharedDataParallel requires one host and matching chunk size/dtype")
         self.exchange_slots = int(exchange_slots)
         # True: the update kernel stores the bf16 weights into every rank's layer buffer itself
         # (peer-mapped stores); False: NCCL all-gather after the kernel.
         self.push_weights = bool(push_weights)
+        # True: exchange and bf16 layer buffers are symmetric-memory allocations with an NVSwitch
+        # multicast address, and fused_update reduces gradients / replicates weights inside the
+        # switch (multimem).  Faster, not bit-exact (see sf_adam_step_sharded_nvls).  Keep it off in
+        # any run where a rank may leave early: its memory stays bound to the multicast object.
+        self.nvls = bool(nvls)
+        self._symm_keep = []                # symmetric-memory tensors and handles kept alive
+        self._mc_base = 0                   # multicast address of the exchange allocation
         self._weight_allocs = []            # (base, peers) of the IPC-visible bf16 layer buffers
         self._views_out = False             # grad_buffer() views exist: the slots must not move any more
         self._cap = 0                       # elements per exchange slot
@@ -188,7 +199,23 @@ class SharedDataParallel:
                 peers.append(out.value)
         return base, peers
 
+    def _symm_alloc(self, nbytes: int):
+        """Collective: a symmetric-memory allocation of `nbytes` on every rank.  Returns (local
+        base pointer, [every rank's base as seen from here], multicast address)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        with torch.cuda.device(self.device):
+            t = symm_mem.empty(int(nbytes), dtype=torch.uint8, device=self.device)
+            hdl = symm_mem.rendezvous(t, dist.group.WORLD)
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        ok = self.ctl.gather(mc != 0)
+        if not all(ok):
+            raise RuntimeError("NVLS multicast is not available on every rank (driver / fabric without multicast support)")
+        self._symm_keep.append((t, hdl))
+        return t.data_ptr(), [int(x) for x in hdl.buffer_ptrs], mc
+
     def _shared_free(self, base, peers):
+        if self.nvls:
+            return   # symmetric-memory tensors are released when close() drops them
         for r, ptr in enumerate(peers):
             if r != self.rank and ptr:
                 self._lib.sf_ipc_close(ptr)
@@ -221,7 +248,10 @@ class SharedDataParallel:
         self._free_exchange()
         elems = -(-elems // 128) * 128
         nbytes = elems * self._esize * self.exchange_slots
-        self._base, self._peer_base = self._shared_alloc(nbytes)
+        if self.nvls:
+            self._base, self._peer_base, self._mc_base = self._symm_alloc(nbytes)
+        else:
+            self._base, self._peer_base = self._shared_alloc(nbytes)
         with torch.cuda.device(self.device):
             flat = torch.as_tensor(_RawCuda(self._base, nbytes), device=self.device)
             flat.zero_()
@@ -260,12 +290,16 @@ class SharedDataParallel:
         dev = self.device
         peer_bf16 = None
         bf16_shard = None
+        mc_bf16 = 0
         if not resident_bf16:
             bf16 = None
             bf16_shard = torch.zeros(s, dtype=torch.bfloat16, device=dev)
         elif self.push_weights and s > 0:
             nbytes = s * self.world_size * 2
-            base, peer_bf16 = self._shared_alloc(nbytes)
+            if self.nvls:
+                base, peer_bf16, mc_bf16 = self._symm_alloc(nbytes)
+            else:
+                base, peer_bf16 = self._shared_alloc(nbytes)
             self._weight_allocs.append((base, peer_bf16))
             with torch.cuda.device(dev):
                 bf16 = torch.as_tensor(_RawCuda(base, nbytes), device=dev).view(torch.bfloat16)
@@ -276,7 +310,8 @@ class SharedDataParallel:
             params=torch.zeros(s, dtype=torch.float32, device=dev),
             exp_avg=torch.zeros(s, dtype=torch.float32, device=dev),
             exp_avg_sq=torch.zeros(s, dtype=torch.float32, device=dev),
-            numel=numel, shard=s, start=a, end=b, bf16=bf16, peer_bf16=peer_bf16, bf16_shard=bf16_shard)
+            numel=numel, shard=s, start=a, end=b, bf16=bf16, peer_bf16=peer_bf16, bf16_shard=bf16_shard,
+            mc_bf16=mc_bf16)
         self._grow_exchange(s * self.world_size)
         self.layers[layer_idx] = state
         return state
@@ -406,6 +441,13 @@ class SharedDataParallel:
                         C.byref(sc), state.params[lo:lo + k].data_ptr(), self._peer_ptrs(slot, a), self.world_size,
                         self._gcode, state.exp_avg[lo:lo + k].data_ptr(), state.exp_avg_sq[lo:lo + k].data_ptr(),
                         state.bf16_shard[lo:lo + k].data_ptr(), k, vec_local, stream))
+                elif state.mc_bf16:
+                    outs = self._push_ptrs(state, a)
+                    _lib.check(self._lib.sf_adam_step_sharded_nvls(
+                        C.byref(sc), state.params[lo:lo + k].data_ptr(),
+                        self._mc_base + (slot * self._cap + a) * self._esize, state.mc_bf16 + 2 * a,
+                        self._peer_ptrs(slot, a), outs, self.world_size, state.exp_avg[lo:lo + k].data_ptr(),
+                        state.exp_avg_sq[lo:lo + k].data_ptr(), k, vec_local, stream))
                 elif state.peer_bf16 is not None:
                     outs = self._push_ptrs(state, a)
                     _lib.check(self._lib.sf_adam_step_sharded_push(
@@ -469,6 +511,10 @@ class SharedDataParallel:
             self._shared_free(base, peers)
         self._weight_allocs = []
         self._cap = 0
+        if self._symm_keep:
+            self._exchange = []
+            self._symm_keep = []
+            self.ctl.barrier()
         self.ctl.close()
 
 
@@ -481,11 +527,12 @@ class ShardedLayerAdam:
 
     def __init__(self, numel: int, device, mode: str = "fused", grad_slots: int = 3, **hp):
         from .layer_adam import LayerAdam
-        if mode not in ("fused", "fused_ag", "nccl"):
-            raise ValueError("mode must be 'fused', 'fused_ag' or 'nccl'")
+        if mode not in ("fused", "fused_ag", "nccl", "nvls"):
+            raise ValueError("mode must be 'fused', 'fused_ag', 'nccl' or 'nvls'")
         self.mode = mode
         self.dp = SharedDataParallel(chunk_numel=max(int(numel), 1), dtype=torch.bfloat16, device=device,
-                                     exchange_slots=grad_slots, push_weights=(mode == "fused"))
+                                     exchange_slots=grad_slots, push_weights=(mode in ("fused", "nvls")),
+                                     nvls=(mode == "nvls"))
         self.adam = LayerAdam(**hp)
         self.state = self.dp.register_layer(0, numel)
         self.numel = int(numel)
@@ -500,13 +547,16 @@ class ShardedLayerAdam:
         if self.mode == "fused":
             return ("one kernel: peer-read fp32 rank-order gradient mean + Adam + bf16 weights pushed to every rank "
                     "over NVLink, stream barriers before and after")
+        if self.mode == "nvls":
+            return ("one kernel: gradient sum reduced inside the NVSwitch (multimem.ld_reduce, bf16 result) + Adam + bf16 "
+                    "weights replicated by the switch (multimem.st), stream barriers before and after; not bit-exact")
         if self.mode == "fused_ag":
             return "fused peer-read fp32 rank-order mean + Adam kernel over NVLink, NCCL bf16 all-gather"
         return "NCCL bf16 reduce-scatter (avg), Adam kernel, NCCL bf16 all-gather"
 
     def step(self, k: int = 0):
         self.group["step"] += 1
-        if self.mode in ("fused", "fused_ag"):
+        if self.mode in ("fused", "fused_ag", "nvls"):
             self.dp.fused_update(0, self.adam, self.group, slot=k)
         else:
             self.dp.nccl_update(0, self.adam, self.group, slot=k)
@@ -538,7 +588,13 @@ class ShardedLayerAdam:
             g = self.group
             _lib.check(dp._lib.sf_adam_scalars(self.adam.optimizer_id, g["step"], g["lr"], g["betas"][0], g["betas"][1],
                                                g["eps"], g["weight_decay"], int(g["bias_correction"] == 1), C.byref(sc)))
-            if k > 0 and st.peer_bf16 is not None:
+            if k > 0 and st.mc_bf16:
+                outs = dp._push_ptrs(st, st.start)
+                _lib.check(dp._lib.sf_adam_step_sharded_nvls(
+                    C.byref(sc), st.params.data_ptr(), dp._mc_base + st.start * 2, st.mc_bf16 + 2 * st.start,
+                    dp._peer_ptrs(0, st.start), outs, dp.world_size, st.exp_avg.data_ptr(), st.exp_avg_sq.data_ptr(),
+                    k, k, torch.cuda.current_stream().cuda_stream))
+            elif k > 0 and st.peer_bf16 is not None:
                 outs = dp._push_ptrs(st, st.start)
                 _lib.check(dp._lib.sf_adam_step_sharded_push(
                     C.byref(sc), st.params.data_ptr(), dp._peer_ptrs(0, st.start), outs, dp.world_size, dp._gcode,
@@ -555,7 +611,7 @@ class ShardedLayerAdam:
             self.adam.step_chunk(st.params[:k], mine, st.exp_avg[:k], st.exp_avg_sq[:k], self.group,
                                  st.bf16[st.start:st.end])
 
-        return self._timed(fused if self.mode in ("fused", "fused_ag") else local, reps)
+        return self._timed(fused if self.mode in ("fused", "fused_ag", "nvls") else local, reps)
 
     def breakdown(self, reps: int) -> dict:
         """Separate device times (ms, max over ranks) of the collectives around the kernel."""

@@ -145,6 +145,54 @@ def _worker(rank, world, path, scenario):
             assert np.allclose(got, ref1[dp2_state.start:dp2_state.end], rtol=0, atol=2.5e-5)  # |step| <= lr, sign may flip on tiny means
             dp.barrier()
             dp.close()
+        elif scenario == "nvls":
+            # in-switch reduction (multimem): not bit-exact by contract.  Expected values: the fp32
+            # rank-order sum rounded once to bf16, divided by world, through the reference update;
+            # the last n mod 8 elements take the exact peer path.
+            from torch._C._distributed_c10d import _SymmetricMemory
+            if not _SymmetricMemory.has_multicast_support(torch._C._autograd.DeviceType.CUDA, rank):
+                return
+            from slideformer_b200.shared_data_parallel import ShardedLayerAdam
+            n = 1_000_003
+            hp = (1e-5, 0.9, 0.999, 1e-8, 0.01)
+            sh = ShardedLayerAdam(numel=n, device=dev, mode="nvls", lr=hp[0], betas=hp[1:3], eps=hp[3], weight_decay=hp[4])
+            gen = torch.Generator().manual_seed(17)
+            p0 = torch.randn(n, generator=gen) * 0.02
+            sh.dp.load_full_params(0, p0.to(dev))
+            orc = O.OracleAdam(*hp, True)
+            p, m, v, o = p0.numpy().copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.uint16)
+            st = sh.state
+            for step in (1, 2, 3):
+                rows = torch.stack([(torch.randn(n, generator=gen) * 1e-3).to(torch.bfloat16) for _ in range(world)])
+                sh.grad_buffer(0).copy_(rows[rank].to(dev))
+                sh.step(0)
+                exact = O.rank_mean(_np_rows(rows))
+                summed = exact * np.float32(world)            # world is a power of two here: exact
+                mean = O.bf16_to_f32(O.f32_to_bf16(summed)) / np.float32(world)
+                # per owner the multicast path covers its slice up to the last multiple of 8 below
+                # the reference call's 16-lane boundary; beyond that the exact peer path runs
+                from slideformer_b200.shared_data_parallel import shard_range, slice_vec_n
+                for r in range(world):
+                    a, b = shard_range(n, world, r)
+                    cut = a + (slice_vec_n(0, n, a, b) & ~7)
+                    mean[cut:b] = exact[cut:b]
+                orc.adam_update(step, *hp, True, p, mean.astype(np.float32), m, v, o)
+            torch.cuda.synchronize()
+            k = st.end - st.start
+            got_p, got_m = st.params[:k].cpu().numpy(), st.exp_avg[:k].cpu().numpy()
+            want_p, want_m = p[st.start:st.end], m[st.start:st.end]
+            # tolerance of the mode: the mean may be off by half a bf16 ulp of the sum
+            gmax = float(np.max(np.abs(mean)))
+            assert np.max(np.abs(got_m - want_m)) <= 3 * 2 ** -8 * gmax, np.max(np.abs(got_m - want_m))
+            assert np.max(np.abs(got_p - want_p)) <= 3 * 2 * hp[0]
+            # (how the switch rounds is not documented: about half of the fp32 results carry the same
+            # bits as this model of it, so only the tolerance above is asserted)
+            full = st.bf16[:n].view(torch.int16).cpu().numpy().view(np.uint16)
+            assert float(np.mean(full == o)) > 0.99                      # every rank holds the whole layer
+            mine = st.bf16[st.start:st.end].view(torch.int16).cpu().numpy().view(np.uint16)
+            assert np.array_equal(mine, O.f32_to_bf16(got_p))            # and the pushed copy is the cast of p
+            sh.dp.barrier()
+            sh.close()
         elif scenario == "host_stepper":
             # gradients in pinned host memory on every rank, bf16 slices back to host, pieces pipelined
             from slideformer_b200.shared_data_parallel import ShardedHostStepper, ShardedLayerAdam
@@ -233,6 +281,12 @@ def test_reference_dp_sequence_sharded(world, scenario):
 def test_medium_layer_fused_and_nccl(world, scenario):
     _need(world)
     _run(world, scenario)
+
+
+def test_nvls_mode_two_ranks():
+    """Needs NVLink multicast (NVSwitch); returns quietly where the driver reports none."""
+    _need(2)
+    _run(2, "nvls")
 
 
 @pytest.mark.parametrize("world", [2, 4])
