@@ -837,21 +837,24 @@ def main_b200(args):
         gc.collect()
         torch.cuda.empty_cache()
         # (model, batch per GPU, seq, timed steps, warm-up, state placement, window mode + meta build)
-        jobs = [("gpt2-small", 8, 1024, 20, 5, "hbm", False), ("llama3.1-8b", 8, 1024, 4, 2, "hbm", False)]
+        # (model, batch per GPU, seq, timed steps, warm-up, state placement, window mode + meta build, HBM budget)
+        jobs = [("gpt2-small", 8, 1024, 20, 5, "hbm", False, None), ("llama3.1-8b", 8, 1024, 4, 2, "hbm", False, None)]
         if world == 1:
-            # the configuration as the benchmark list words it: host-pinned optimizer state
-            jobs.append(("llama3.1-8b", 8, 1024, 2, 1, "host", False))
+            # the configuration as the benchmark list words it: host-pinned optimizer state ...
+            jobs.append(("llama3.1-8b", 8, 1024, 2, 1, "host", False, None))
+            # ... and the middle ground: state in HBM while a 64 GB budget lasts, the rest streamed
+            jobs.append(("llama3.1-8b", 8, 1024, 2, 1, "auto", False, 64.0))
         if world == 8:
             # Llama-3.1-70B: state sharded 1/8, bf16 weights kept as slices and gathered per layer
-            jobs.append(("llama3.1-70b", 4, 2048, 2, 1, "hbm", True))
+            jobs.append(("llama3.1-70b", 4, 2048, 2, 1, "hbm", True, None))
         finetune = []
-        for name, fbatch, fseq, fsteps, fwarm, state_dev, window in jobs:
+        for name, fbatch, fseq, fsteps, fwarm, state_dev, window, budget in jobs:
             dp = None
             if world > 1:
                 from slideformer_b200.shared_data_parallel import SharedDataParallel
                 dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=2)
             finetune.append(run_finetune(name, fbatch, fseq, fsteps, fwarm, dev, world, rank, dp, state_device=state_dev,
-                                         weight_window=window, meta=window))
+                                         weight_window=window, meta=window, hbm_state_budget_gb=budget))
             if dp is not None:
                 dp.close()
 

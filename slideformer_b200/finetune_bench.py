@@ -37,7 +37,7 @@ def model_flops_per_step(cfg, batch, seq):
 def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int, dev, world: int = 1, rank: int = 0,
                  dp=None, layers=None, state_device: str = "hbm", activation_offload: str = "hbm",
                  activation_checkpoint: bool = True, double_buffer: bool = False, lr: float = 1e-5,
-                 weight_window: bool = False, meta: bool = False) -> dict:
+                 weight_window: bool = False, meta: bool = False, hbm_state_budget_gb=None) -> dict:
     """Build the random-init model, run warm-up + timed steps, return the result line as a dict.
     `dp` is a SharedDataParallel (state sharded over the ranks of the default process group) or None."""
     from slideformer_b200 import _lib
@@ -52,8 +52,10 @@ def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int,
         model, dev, torch.bfloat16, double_buffer=double_buffer, enable_timing=True, enable_memory_stats=False,
         optimizer_kwargs=dict(lr=lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01),
         shared_dp=dp, state_device=state_device, activation_offload=activation_offload,
-        activation_checkpoint=activation_checkpoint, weight_window=weight_window)
+        activation_checkpoint=activation_checkpoint, weight_window=weight_window,
+        hbm_state_budget_gb=hbm_state_budget_gb)
     torch.cuda.synchronize()
+    placement = engine.state_placement
     build_s = time.perf_counter() - t_build
 
     vocab = model.config.vocab_size
@@ -102,6 +104,9 @@ def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int,
             "config": {"workload": f"{model_name} full fine-tune, layer sliding", "global_batch": batch * world,
                        "seq_len": seq, "state_device": state_device, "activation_offload": activation_offload,
                        "activation_checkpoint": activation_checkpoint, "weight_window": weight_window,
+                       "hbm_state_budget_gb": hbm_state_budget_gb,
+                       "units_with_state_in_hbm": (placement.count("hbm") if placement is not None else None),
+                       "units": len(engine.transformer_layers),
                        "parallelism": f"dp{world} sharded state" if dp is not None else "single GPU"},
             "model_tflops": flops / (ms * 1e-3) / 1e12, "params": sum(u.total_size for u in engine.transformer_layers),
             "optimizer_ms_per_step": sum(upd.values()),
@@ -148,7 +153,9 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=None, help="override the number of decoder layers")
-    ap.add_argument("--state-device", default="hbm", choices=["hbm", "host"])
+    ap.add_argument("--state-device", default="hbm", choices=["hbm", "host", "auto"])
+    ap.add_argument("--hbm-state-budget-gb", type=float, default=None,
+                    help="with --state-device auto: HBM the fp32 state may take; units beyond it keep their state in pinned host memory")
     ap.add_argument("--activation-offload", default="hbm", choices=["hbm", "host"])
     ap.add_argument("--no-ckpt", action="store_true", help="keep all activations instead of checkpointing each layer")
     ap.add_argument("--double-buffer", action="store_true")
@@ -173,7 +180,7 @@ def main(argv=None):
         dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=3 if args.double_buffer else 2)
     line = run_finetune(args.model, args.batch, args.seq, args.steps, args.warmup, dev, world, rank, dp, args.layers,
                         args.state_device, args.activation_offload, not args.no_ckpt, args.double_buffer, args.lr,
-                        args.weight_window, args.meta)
+                        args.weight_window, args.meta, args.hbm_state_budget_gb)
     if rank == 0:
         print(json.dumps(line))
         if args.csv:

@@ -34,6 +34,36 @@ from .shared_data_parallel import shard_numel
 from .transformer_layer import GradUnitPool, WeightUnitPool, split_transformer_model
 
 
+def unit_numels(parts) -> list:
+    """Parameters per streamed unit, in unit order: embedding, decoder layers, norm + head (a tied
+    head weight counts once, in the embedding unit)."""
+    def count(mods, skip=()):
+        seen, total = set(id(s) for s in skip), 0
+        for mod in mods:
+            for p in mod.parameters():
+                if id(p) not in seen:
+                    seen.add(id(p))
+                    total += p.numel()
+        return total
+    tied = [parts.tied_param] if parts.tied_param is not None else []
+    return [count([parts.embed])] + [count([layer]) for layer in parts.layers] + [count([parts.norm, parts.lm_head], tied)]
+
+
+def plan_state_placement(unit_sizes, budget_bytes: int) -> list:
+    """'hbm' or 'host' per unit: units keep their fp32 master weights and both Adam moments
+    (12 bytes per parameter) in HBM, in unit order, while the budget lasts; the rest live in
+    pinned host memory and are streamed through the GPU by the update."""
+    placement, used = [], 0
+    for n in unit_sizes:
+        need = 12 * int(n)
+        if used + need <= budget_bytes:
+            placement.append("hbm")
+            used += need
+        else:
+            placement.append("host")
+    return placement
+
+
 class CausalLMOutput(dict):
     """Minimal stand-in for transformers' CausalLMOutputWithPast (attribute and key access)."""
 
@@ -50,7 +80,8 @@ class SlideFormerOffloader(nn.Module):
                  enable_memory_stats: bool = True, optimizer_kwargs: Optional[dict] = None,
                  auto_backward_in_forward: bool = True, shared_dp=None, *, state_device: str = "hbm",
                  activation_offload: str = "hbm", activation_checkpoint: bool = True, loss_chunk_tokens: int = 4096,
-                 update_chunk: Optional[int] = None, weight_window: bool = False):
+                 update_chunk: Optional[int] = None, weight_window: bool = False,
+                 hbm_state_budget_gb: Optional[float] = None, enable_nvtx: bool = True):
         super().__init__()
         if not isinstance(device, torch.device):
             raise TypeError("device must be torch.device")
@@ -62,6 +93,10 @@ class SlideFormerOffloader(nn.Module):
             raise NotImplementedError("NVMe activation offload is not part of this build; use activation_offload='host'")
         if activation_offload not in ("hbm", "host"):
             raise ValueError("activation_offload must be 'hbm' or 'host'")
+        if state_device not in ("hbm", "host", "auto"):
+            raise ValueError("state_device must be 'hbm', 'host' or 'auto'")
+        if state_device == "auto" and shared_dp is not None:
+            raise ValueError("state_device='auto' applies to one GPU; sharded state is always HBM-resident")
         self.device, self.dtype = device, dtype
         self.double_buffer = double_buffer
         self.auto_backward_in_forward = auto_backward_in_forward
@@ -95,16 +130,36 @@ class SlideFormerOffloader(nn.Module):
         self.weight_window = bool(weight_window)
         self.weight_pool = self.comm_stream = None
         if self.weight_window:
-            if shared_dp is None:
-                raise ValueError("weight_window needs shared_dp (sharded optimizer state)")
+            # with shared_dp: bf16 slices stay resident and a unit is all-gathered into the window;
+            # on one GPU: the bf16 weights wait in pinned host memory and are copied into the window
             with torch.cuda.device(device):
                 self.comm_stream = torch.cuda.Stream()
-            unit_elems = shard_numel(self.max_param_size, shared_dp.world_size) * shared_dp.world_size
-            self.weight_pool = WeightUnitPool(3 if double_buffer else 2, unit_elems, dtype, device)
+            if shared_dp is not None:
+                unit_elems = shard_numel(self.max_param_size, shared_dp.world_size) * shared_dp.world_size
+            else:
+                unit_elems = -(-self.max_param_size // 128) * 128
+            self.weight_pool = WeightUnitPool(3 if double_buffer else 2, unit_elems, dtype, device,
+                                              with_stage=shared_dp is None)
+        # where each unit's fp32 state lives: everywhere the same, or planned against an HBM budget
+        self.state_placement = None
+        if state_device == "auto":
+            sizes = unit_numels(self.parts)
+            if hbm_state_budget_gb is None:
+                free = torch.cuda.mem_get_info(device)[0]
+                resident_weights = 0 if self.weight_window else 2 * sum(sizes)
+                reserve = resident_weights + n_units * 2 * max(sizes) + (24 << 30)   # weights, gradient ring, activations
+                budget = max(0, int(0.9 * (free - reserve)))
+            else:
+                budget = int(hbm_state_budget_gb * (1 << 30))
+            self.state_placement = plan_state_placement(sizes, budget)
+            self.hbm_state_budget_bytes = budget
         kwargs = dict(weight_pool=self.weight_pool, comm_stream=self.comm_stream,
                       opt_stream=self.opt_stream, enable_timing=enable_timing, layer_optimizer=self.layer_optimizer,
-                      state_device=state_device, shared_dp=shared_dp, activation_checkpoint=activation_checkpoint,
-                      loss_chunk_tokens=loss_chunk_tokens)
+                      state_device=("hbm" if state_device == "auto" else state_device), shared_dp=shared_dp,
+                      activation_checkpoint=activation_checkpoint, loss_chunk_tokens=loss_chunk_tokens,
+                      enable_nvtx=enable_nvtx)
+        if self.state_placement is not None:
+            kwargs["state_devices"] = self.state_placement
         if update_chunk is not None:
             kwargs["update_chunk"] = update_chunk
         comps = split_transformer_model(self.parts, device, dtype, **kwargs)
@@ -131,6 +186,7 @@ class SlideFormerOffloader(nn.Module):
         last = len(units) - 1
 
         def pre_forward(module, args):
+            module.begin_forward_span()
             if self.weight_window:
                 module.to_device_async()                       # no-op if the prefetch already took a unit
                 if module.layer_idx < last:
@@ -140,16 +196,18 @@ class SlideFormerOffloader(nn.Module):
             return None
 
         def post_forward(module, args, output):
+            module.end_forward_span()
             # the output unit keeps its weights: its backward starts right away
             if self.weight_window and (module.layer_idx < last or not torch.is_grad_enabled()):
                 module.release_weights()
             return None
 
         def pre_backward(module, grad_output):
+            module.begin_backward_span()
             module.to_device_async(is_bwd=True)
             if self.weight_window:
                 if module.layer_idx > 1:
-                    units[module.layer_idx - 1].to_device_async()   # prefetch the previous unit's weights
+                    units[module.layer_idx - 1].to_device_async(bwd_phase=True)   # prefetch the previous unit's weights
                 module.wait_for_h2d()
             return None
 
@@ -174,6 +232,7 @@ class SlideFormerOffloader(nn.Module):
             self.activation_store.reset()
             return
         self.activation_store = ActivationStore(len(self.decoder_layers), sig, self.dtype, self.device)
+        self.activation_store.timing = bool(self.enable_timing)
         for unit in self.transformer_layers[1:-1]:
             unit.activation_store = self.activation_store
         self._activation_layout_signature = sig
@@ -243,30 +302,51 @@ class SlideFormerOffloader(nn.Module):
         dp.barrier()
         return output_dir
 
+    def layer_timings_ms(self, show_history: bool = False):
+        """{operation: [ms per unit]} from the recorded CUDA-event spans (needs enable_timing): the
+        most recent step's span of every unit, or with show_history each unit's mean over all steps.
+        Activation-copy spans come from the activation store when activations go to host memory."""
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for u in self.transformer_layers:
+            for op, spans in u.timings.items():
+                if spans:
+                    used = spans if show_history else spans[-1:]
+                    out.setdefault(op, []).append((u.layer_idx, sum(a.elapsed_time(b) for a, b in used) / len(used), len(used)))
+        store = self.activation_store
+        if store is not None:
+            for op, spans in (("ac_fwd_d2h", store.spans_d2h), ("ac_bwd_h2d", store.spans_h2d)):
+                done = [(a, b) for a, b in spans if b.query()]
+                if done:
+                    used = done if show_history else done[-len(self.decoder_layers):]
+                    out[op] = [(None, sum(a.elapsed_time(b) for a, b in used) / len(used), len(used))]
+        return out
+
     def print_layer_stats(self, layer_idx=None, show_history: bool = False):
-        """Per-unit device time of the optimizer step under the reference's label "parameter update"
-        (offload_transformer.py:337-377).  show_history averages over all recorded steps, otherwise
-        the most recent step is shown; the transfer labels of the reference have no counterpart
-        because nothing is transferred."""
+        """Per-unit device times under the reference's labels (offload_transformer.py:337-377,
+        utils/timer.py:11-21): forward, backward, parameter update, the weight-window fill as
+        "h2d transfer fw / bw", and the activation copies as "ac fwd d2h" / "ac bwd h2d".
+        show_history averages over all recorded steps, otherwise the most recent step is shown."""
         if not self.enable_timing:
             return
-        torch.cuda.synchronize(self.device)
-        rows = []
-        for u in self.transformer_layers:
-            if layer_idx is not None and u.layer_idx != layer_idx:
-                continue
-            spans = u.timings["parameter_update"]
-            if spans:
-                used = spans if show_history else spans[-1:]
-                rows.append((u.layer_idx, sum(a.elapsed_time(b) for a, b in used) / len(used), len(used)))
-        if not rows:
+        from .transformer_layer import format_timing_label
+        stats = self.layer_timings_ms(show_history)
+        if not stats:
+            return
+        if layer_idx is not None:
+            print(f"\nLayer {layer_idx} Statistics:")
+            for op, rows in stats.items():
+                for idx, ms, calls in rows:
+                    if idx == layer_idx:
+                        print(f"  {format_timing_label(op)}: {ms:.2f}ms ({calls} calls)")
             return
         print("\nHistorical Average Layer Statistics:" if show_history else "\nCurrent Step Layer Statistics:")
-        if layer_idx is None:
+        for op, rows in stats.items():
             mean = sum(r[1] for r in rows) / len(rows)
-            print(f"  parameter update: {mean:.2f}ms (avg across {len(rows)} layers)")
-        else:
-            print(f"  parameter update: {rows[0][1]:.2f}ms (layer {layer_idx}, {rows[0][2]} calls)")
+            if show_history:
+                print(f"  {format_timing_label(op)}: {mean:.2f}ms (avg over {sum(r[2] for r in rows)} calls)")
+            else:
+                print(f"  {format_timing_label(op)}: {mean:.2f}ms (avg across {len(rows)} layers)")
 
     def save_pretrained(self, output_dir):
         """Write HF-format weights cast to the compute dtype (offload_transformer.py:593-597).  The
@@ -278,6 +358,17 @@ class SlideFormerOffloader(nn.Module):
         the slices are all-gathered first, which needs every rank), and a second barrier releases
         them."""
         self.wait_for_completion()
+        if self.weight_window and self.shared_dp is None:
+            # one-GPU window: the weights live in each unit's pinned host store
+            names = {id(p): n for n, p in self.base_model.named_parameters()}
+            state = {}
+            for unit in self.transformer_layers:
+                flat = unit.bf16_weights_flat()
+                for local, p in unit._managed_named_params:
+                    off, shape, k = unit._param_maps[local]
+                    state[names[id(p)]] = flat[off:off + k].view(shape).clone()
+            self.base_model.save_pretrained(output_dir, state_dict=state)
+            return output_dir
         if self.weight_window:
             self.shared_dp.barrier()
             return self._save_from_slices(output_dir)

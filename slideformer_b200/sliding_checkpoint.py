@@ -40,6 +40,28 @@ class ActivationStore:
         self.pool_free = [torch.cuda.Event() for _ in range(pool_size)]   # compute finished reading the buffer
         self.bytes_d2h = 0
         self.bytes_h2d = 0
+        # CUDA-event pairs around the copies, filled only when `timing` is set by the engine:
+        # the reference's "ac fwd d2h" / "ac bwd h2d" timer labels (utils/timer.py:19-20)
+        self.timing = False
+        self.spans_d2h: List[tuple] = []
+        self.spans_h2d: List[tuple] = []
+
+    def _span(self, bucket, name):
+        """Start an optional timing span + NVTX range on the store's stream; returns a closer."""
+        if not self.timing:
+            return lambda: None
+        t0 = torch.cuda.Event(enable_timing=True)
+        t0.record(self.stream)
+        rid = torch.cuda.nvtx.range_start(name)
+
+        def close():
+            t1 = torch.cuda.Event(enable_timing=True)
+            t1.record(self.stream)
+            bucket.append((t0, t1))
+            if len(bucket) > 4096:
+                del bucket[:2048]
+            torch.cuda.nvtx.range_end(rid)
+        return close
 
     def next_buffer(self):
         i = self.pool_idx % len(self.pool)
@@ -69,7 +91,9 @@ class SlidingCheckpoint(saved_tensors_hooks):
             ready.record(cur)
             with torch.cuda.stream(store.stream):
                 store.stream.wait_event(ready)
+                close = store._span(store.spans_d2h, f"AC_D2H_Layer_{layer_idx}")
                 host.copy_(t, non_blocking=True)
+                close()
                 store.saved[self.i].record(store.stream)
             t.record_stream(store.stream)
             store.bytes_d2h += host.numel() * host.element_size()
@@ -85,7 +109,9 @@ class SlidingCheckpoint(saved_tensors_hooks):
             with torch.cuda.stream(store.stream):
                 store.stream.wait_event(store.pool_free[k])   # previous reader of this buffer is done
                 store.stream.wait_event(store.saved[layer])
+                close = store._span(store.spans_h2d, f"AC_H2D_Layer_{layer + 1}")
                 buf.copy_(store.host[layer], non_blocking=True)
+                close()
                 done.record(store.stream)
             store.bytes_h2d += buf.numel() * buf.element_size()
             store.fifo.append((layer, k, buf, done))

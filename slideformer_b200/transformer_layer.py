@@ -38,6 +38,51 @@ from .sliding_checkpoint import SlidingCheckpoint
 # Optimizer chunk, in elements: the reference's D2H chunk (transformer_layer.py:26-27).
 UPDATE_CHUNK_SIZE = 32 * 1024 * 1024
 
+# Operations timed per unit and how they are printed (utils/timer.py:11-21).  There is no
+# gradient or weight D2H on this path, so the reference's two "d2h transfer" labels never get a
+# sample here; "h2d transfer fw / bw" time the weight-window fill (all-gather or host copy).
+TIMING_LABELS = {
+    "h2d_transfer_fw": "h2d transfer fw",
+    "h2d_transfer_bw": "h2d transfer bw",
+    "d2h_transfer_fw": "d2h transfer fw",
+    "d2h_transfer_bw": "d2h transfer bw",
+    "forward": "forward",
+    "backward": "backward",
+    "parameter_update": "parameter update",
+    "ac_fwd_d2h": "ac fwd d2h",
+    "ac_bwd_h2d": "ac bwd h2d",
+}
+
+
+def format_timing_label(operation: str) -> str:
+    return TIMING_LABELS.get(operation, operation.replace("_", " "))
+
+
+class _Span:
+    """A CUDA-event pair on one stream plus an NVTX range on the host thread, both optional."""
+
+    def __init__(self, unit, op: str, nvtx_name: Optional[str], stream):
+        self.unit, self.op, self.stream = unit, op, stream
+        # start/end ranges rather than push/pop: the phases of neighbouring units overlap in time
+        self.nvtx = torch.cuda.nvtx.range_start(nvtx_name) if (unit.enable_nvtx and nvtx_name) else None
+        self.t0 = None
+        if unit.enable_timing:
+            self.t0 = torch.cuda.Event(enable_timing=True)
+            self.t0.record(stream)
+
+    def close(self):
+        if self.t0 is not None:
+            t1 = torch.cuda.Event(enable_timing=True)
+            t1.record(self.stream)
+            spans = self.unit.timings.setdefault(self.op, [])
+            spans.append((self.t0, t1))
+            if len(spans) > 4096:
+                del spans[:2048]
+            self.t0 = None
+        if self.nvtx is not None:
+            torch.cuda.nvtx.range_end(self.nvtx)
+            self.nvtx = None
+
 
 class GradUnitPool:
     """The gradient side of the reference's GPU cache units (offload_transformer.py:205-219):
@@ -65,13 +110,16 @@ class WeightUnitPool:
     buffers that a layer's slices are all-gathered into shortly before the layer runs.  `free`
     is recorded on the compute stream after the last kernel that read the unit."""
 
-    def __init__(self, num_units: int, numel: int, dtype, device):
+    def __init__(self, num_units: int, numel: int, dtype, device, with_stage: bool = False):
         self.units = []
         for _ in range(num_units):
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream(device))
             self.units.append({"param": torch.empty(numel, dtype=dtype, device=device), "free": ev})
         self._next = 0
+        # one-GPU window: the optimizer writes a unit's new bf16 weights here before they go to the
+        # unit's pinned host store; every use is on the optimizer stream, so one buffer serves all units
+        self.stage = torch.empty(numel, dtype=dtype, device=device) if with_stage else None
 
     def get(self):
         u = self.units[self._next % len(self.units)]
@@ -100,7 +148,7 @@ class OffloadLayerWrapper(nn.Module):
                  tied_param: Optional[nn.Parameter] = None, enable_timing: bool = False, is_last_layer: bool = False,
                  layer_optimizer=None, dtype: torch.dtype = torch.bfloat16, state_device: str = "hbm",
                  shared_dp=None, update_chunk: int = UPDATE_CHUNK_SIZE, weight_pool: Optional[WeightUnitPool] = None,
-                 comm_stream: Optional[torch.cuda.Stream] = None, init_seed: int = 0):
+                 comm_stream: Optional[torch.cuda.Stream] = None, init_seed: int = 0, enable_nvtx: bool = True):
         super().__init__()
         if layer_optimizer is None:
             raise RuntimeError("a shared LayerAdam must be provided")
@@ -115,6 +163,8 @@ class OffloadLayerWrapper(nn.Module):
         self.shared_dp = shared_dp
         self.update_chunk = int(update_chunk)
         self.enable_timing = enable_timing
+        self.enable_nvtx = enable_nvtx
+        self._fw_span = self._bw_span = None
         self.skip_params = skip_params or set()
         self.tied_param = tied_param
         self._is_tied_output = tied_param is not None and tied_param in self.skip_params
@@ -125,6 +175,7 @@ class OffloadLayerWrapper(nn.Module):
         self._update_recorded = False
         self._unit = None
         self._pending = 0          # parameters whose gradient has not been accumulated yet
+        self._in_backward = False
         self.timings: Dict[str, List] = {"parameter_update": []}
         self.host_update_seconds = 0.0   # host time spent enqueueing optimizer steps (not device time)
 
@@ -132,8 +183,9 @@ class OffloadLayerWrapper(nn.Module):
         self.comm_stream = comm_stream
         self.weights_ready = torch.cuda.Event()
         self._wunit = None
-        if weight_pool is not None and (shared_dp is None or tied_param is not None):
-            raise ValueError("the weight window needs sharded state (shared_dp) and untied embeddings")
+        if weight_pool is not None and tied_param is not None:
+            raise ValueError("the weight window needs untied embeddings")
+        self._bf16_host = None   # one-GPU window mode: the permanent bf16 weights, in pinned host memory
 
         # parameters that exist only on the meta device are created here, directly in their final place
         gen = torch.Generator(device=device).manual_seed(1000003 * init_seed + layer_idx)
@@ -163,7 +215,14 @@ class OffloadLayerWrapper(nn.Module):
                 self._params_flat = torch.empty(n, dtype=torch.float32, device=device)
             else:
                 self._params_flat = pinned_empty(n, torch.float32, device)
-            self._bf16_flat = torch.empty(n, dtype=dtype, device=device)
+            if weight_pool is None:
+                self._bf16_flat = torch.empty(n, dtype=dtype, device=device)
+            else:
+                # one-GPU weight window (the reference's headline mode, offload_transformer.py:75-79,
+                # transformer_layer.py:273-335): the bf16 weights wait in pinned host memory and are
+                # copied into a window unit one unit ahead of the compute stream
+                self._bf16_flat = None
+                self._bf16_host = pinned_empty(n, dtype, device)
 
         self._param_maps = OrderedDict()
         self._master_views = []
@@ -187,6 +246,8 @@ class OffloadLayerWrapper(nn.Module):
                     self._bf16_flat[off:off + k].copy_(src)
                     p.data = self._bf16_flat[off:off + k].view(shape)   # the weights the layer computes with
                 else:
+                    if self._bf16_host is not None:
+                        self._bf16_host[off:off + k].copy_(src.to(dtype))
                     p.data = torch.empty(0, dtype=dtype, device=device)  # pointed into a window unit on demand
                 p.grad = None
                 off += k
@@ -197,11 +258,13 @@ class OffloadLayerWrapper(nn.Module):
             else:
                 off = 0
                 for name, p in self._managed_named_params:
-                    k = p.numel()
-                    self._master_views.append(nn.Parameter(self._params_flat[off:off + k].view(p.shape), requires_grad=False))
-                    self._bf16_views.append(self._bf16_flat[off:off + k].view(p.shape))
+                    _, shape, k = self._param_maps[name]
+                    self._master_views.append(nn.Parameter(self._params_flat[off:off + k].view(shape), requires_grad=False))
+                    if self._bf16_flat is not None:
+                        self._bf16_views.append(self._bf16_flat[off:off + k].view(shape))
                     off += k
-                self.layer_optimizer.add_layer_params(layer_idx, self._master_views, self._bf16_views)
+                self.layer_optimizer.add_layer_params(layer_idx, self._master_views,
+                                                      self._bf16_views if self._bf16_flat is not None else None)
         for module in layer.modules():   # constants stay on the compute device (transformer_layer.py:148-152)
             for bname, buf in module.named_buffers(recurse=False):
                 if buf is not None and not buf.is_meta and buf.device != device:
@@ -211,12 +274,12 @@ class OffloadLayerWrapper(nn.Module):
                 p.register_post_accumulate_grad_hook(self._on_param_grad)
 
     # ---- window management (names of transformer_layer.py:273-343) ------------------------------
-    def to_device_async(self, is_bwd: bool = False):
+    def to_device_async(self, is_bwd: bool = False, bwd_phase: Optional[bool] = None):
         """Forward needs nothing (the bf16 weights are resident).  For backward: take the next
         gradient unit, wait until the optimizer has released it, zero it and point every
         parameter's .grad into it, so autograd accumulates straight into the flat buffer."""
         if self.weight_pool is not None and self._wunit is None and not (is_bwd and isinstance(self, EmbeddingWrapper)):
-            self._acquire_weights()
+            self._acquire_weights(is_bwd if bwd_phase is None else bwd_phase)
         if not is_bwd or self._unit is not None:
             return
         unit = self.grad_pool.get()
@@ -232,7 +295,7 @@ class OffloadLayerWrapper(nn.Module):
                 self._pending += 1
         self._unit = unit
 
-    def _acquire_weights(self):
+    def _acquire_weights(self, is_bwd: bool = False):
         """Window mode: all-gather this unit's bf16 slices into the next window unit on the
         communication stream (behind the unit's last optimizer step and the unit's previous
         reader) and point the parameters into it (the counterpart of the reference's H2D task,
@@ -241,9 +304,14 @@ class OffloadLayerWrapper(nn.Module):
         cs = self.comm_stream
         with torch.cuda.stream(cs):
             cs.wait_event(unit["free"])
+            span = _Span(self, "h2d_transfer_bw" if is_bwd else "h2d_transfer_fw", f"H2D_Layer_{self.layer_idx}", cs)
             if self._update_recorded:
                 cs.wait_event(self.update_done)
-            self.shared_dp.gather_weights(self.layer_idx, unit["param"])
+            if self.shared_dp is not None:
+                self.shared_dp.gather_weights(self.layer_idx, unit["param"])
+            else:
+                unit["param"][: self.total_size].copy_(self._bf16_host, non_blocking=True)
+            span.close()
             self.weights_ready.record(cs)
         for name, p in self._managed_named_params:
             off, shape, k = self._param_maps[name]
@@ -265,9 +333,32 @@ class OffloadLayerWrapper(nn.Module):
         reference handing the unit to its D2H worker)."""
         if is_bwd:
             self.compute_ready_bw.record(torch.cuda.current_stream(self.device))
+            self.end_backward_span()
 
     def wait_for_d2h(self):
         return None
+
+    # ---- timing / NVTX ranges of the compute phases (names of transformer_layer.py:524, offload_transformer.py:262)
+    def begin_forward_span(self):
+        if self.enable_timing or self.enable_nvtx:
+            self._fw_span = _Span(self, "forward", f"Forward_Layer_{self.layer_idx}", torch.cuda.current_stream(self.device))
+
+    def end_forward_span(self):
+        if self._fw_span is not None:
+            self._fw_span.close()
+            self._fw_span = None
+
+    def begin_backward_span(self):
+        self._in_backward = True
+        if (self.enable_timing or self.enable_nvtx) and self._bw_span is None:
+            self._bw_span = _Span(self, "backward", f"Backward_Compute_Layer_{self.layer_idx}",
+                                  torch.cuda.current_stream(self.device))
+
+    def end_backward_span(self):
+        self._in_backward = False
+        if self._bw_span is not None:
+            self._bw_span.close()
+            self._bw_span = None
 
     def _on_param_grad(self, _param):
         if self._unit is None:
@@ -296,12 +387,9 @@ class OffloadLayerWrapper(nn.Module):
         g = unit["grad"]
         opt = self.layer_optimizer
         s = self.opt_stream
-        t0 = t1 = None
         with torch.cuda.stream(s):
             s.wait_event(self.compute_ready_bw)
-            if self.enable_timing:
-                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                t0.record(s)
+            span = _Span(self, "parameter_update", f"Update_Layer_{self.layer_idx}", s)
             if self.shared_dp is not None:
                 if self._dp_group is None:
                     self._dp_group = dict(opt.defaults, step=0)
@@ -318,19 +406,20 @@ class OffloadLayerWrapper(nn.Module):
             else:
                 group = opt.begin_chunk_step(self.layer_idx)
                 m, v = opt.exp_avg_flat[self.layer_idx], opt.exp_avg_sq_flat[self.layer_idx]
+                bf16_out = self._bf16_flat if self._bf16_flat is not None else self.weight_pool.stage[:n]
                 if self.state_device == "hbm":
                     for cs in range(0, n, self.update_chunk):
                         ce = min(cs + self.update_chunk, n)
-                        opt.step_chunk(self._params_flat[cs:ce], g[cs:ce], m[cs:ce], v[cs:ce], group, self._bf16_flat[cs:ce])
+                        opt.step_chunk(self._params_flat[cs:ce], g[cs:ce], m[cs:ce], v[cs:ce], group, bf16_out[cs:ce])
                 else:
                     # host-resident state: chunked and double-buffered inside the library, one
                     # reference call per chunk like the reference's chunk consumer
-                    opt.step_chunk(self._params_flat, g[:n], m, v, group, self._bf16_flat,
+                    opt.step_chunk(self._params_flat, g[:n], m, v, group, bf16_out,
                                    host_chunk_calls=True, host_chunk_numel=self.update_chunk)
                 opt.end_chunk_step(self.layer_idx)
-            if self.enable_timing:
-                t1.record(s)
-                self.timings["parameter_update"].append((t0, t1))
+                if self._bf16_host is not None:
+                    self._bf16_host.copy_(bf16_out, non_blocking=True)   # the next prefetch reads it from here
+            span.close()
             self.update_done.record(s)
             unit["reuse_ready"].record(s)
         self._update_recorded = True
@@ -351,6 +440,15 @@ class OffloadLayerWrapper(nn.Module):
                 raise NotImplementedError("gathering fp32 masters from window-mode shards is not implemented")
             return self._bf16_flat.float()
         return self._params_flat.to(self.device)
+
+    def bf16_weights_flat(self) -> torch.Tensor:
+        """This unit's current bf16 weights as one flat tensor (device-resident, or the pinned host
+        store in one-GPU window mode).  Sharded window mode keeps only slices: gather them instead."""
+        if self._bf16_flat is not None:
+            return self._bf16_flat
+        if self._bf16_host is not None:
+            return self._bf16_host
+        raise RuntimeError("only slices of this unit's bf16 weights are resident; all-gather them")
 
     def forward(self, *args, **kwargs):
         raise NotImplementedError
@@ -449,15 +547,20 @@ def split_transformer_model(parts: TextModelParts, device: torch.device, dtype: 
     by the output unit; autograd sums both uses before the owner's gradient hook fires."""
     activation_checkpoint = kwargs.pop("activation_checkpoint", True)
     loss_chunk_tokens = kwargs.pop("loss_chunk_tokens", 4096)
+    placement = kwargs.pop("state_devices", None)   # optional per-unit "hbm" / "host", overrides state_device
     tied = parts.tied_param
-    units = nn.ModuleList([])
-    units.append(EmbeddingWrapper(parts.embed, device, 0, dtype=dtype, tied_param=tied, **kwargs))
     L = len(parts.layers)
+
+    def kw(idx):
+        return dict(kwargs, state_device=placement[idx]) if placement is not None else kwargs
+
+    units = nn.ModuleList([])
+    units.append(EmbeddingWrapper(parts.embed, device, 0, dtype=dtype, tied_param=tied, **kw(0)))
     for idx, layer in enumerate(parts.layers, start=1):
         units.append(DecoderWrapper(layer, device, idx, dtype=dtype, is_last_layer=(idx == L),
-                                    activation_checkpoint=activation_checkpoint, **kwargs))
+                                    activation_checkpoint=activation_checkpoint, **kw(idx)))
     units.append(OutputWrapper(parts.norm, parts.lm_head, device, L + 1, dtype=dtype,
                                softcap=getattr(parts.config, "final_logit_softcapping", None),
                                skip_params={tied} if tied is not None else None, tied_param=tied,
-                               loss_chunk_tokens=loss_chunk_tokens, **kwargs))
+                               loss_chunk_tokens=loss_chunk_tokens, **kw(L + 1)))
     return {"transformer_layers": units, "rotary_emb": parts.rotary_emb}

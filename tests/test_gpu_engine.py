@@ -181,6 +181,86 @@ def test_host_state_keeps_the_reference_call_history_per_chunk(oracle):
         assert np.array_equal(_bits(ub._bf16_flat), _bits(uo._bf16_flat))
 
 
+def _train(eng, ids):
+    for x in ids:
+        eng(x, labels=x).loss.backward()
+        eng.wait_for_completion()
+
+
+@pytest.mark.parametrize("kw", [dict(weight_window=True), dict(weight_window=True, state_device="host"),
+                                dict(weight_window=True, double_buffer=True)])
+def test_one_gpu_weight_window_matches_resident_weights(kw, tmp_path):
+    """bf16 weights parked in pinned host memory and copied into a 2- or 3-unit window one unit
+    ahead (the reference's headline mode, offload_transformer.py:75-79): same bits as keeping
+    every layer's bf16 weights in HBM, and no unit holds a device-resident copy."""
+    base, _ = _make("llama-tiny")
+    win, _ = _make("llama-tiny", **kw)
+    ids = _ids(base.config.vocab_size, 2, 32, 3, seed=12)
+    _train(base, ids)
+    _train(win, ids)
+    for ub, uw in zip(base.transformer_layers, win.transformer_layers):
+        assert uw._bf16_flat is None and uw._bf16_host.is_pinned()
+        assert np.array_equal(_bits(ub._params_flat.to(DEV)), _bits(uw._params_flat.to(DEV))), ub.layer_idx
+        assert np.array_equal(_bits(ub._bf16_flat), _bits(uw.bf16_weights_flat().to(DEV))), ub.layer_idx
+    # inference after training uses the window too
+    with torch.no_grad():
+        a, b = base(ids[0]).logits.float(), win(ids[0]).logits.float()
+    assert torch.equal(a, b)
+    from transformers import AutoModelForCausalLM
+    out = win.save_pretrained(str(tmp_path / "ckpt"))
+    again = AutoModelForCausalLM.from_pretrained(out, dtype=torch.bfloat16).to(DEV)
+    with torch.no_grad():
+        assert (again(input_ids=ids[0]).logits.float() - a).abs().max().item() < 0.1
+
+
+def test_auto_state_placement_splits_units_between_hbm_and_host():
+    """state_device='auto' with a small HBM budget: the first units keep their fp32 state in HBM,
+    the rest stream it from pinned host memory; the result has the bits of the all-HBM run."""
+    from slideformer_b200.offload_transformer import plan_state_placement, unit_numels
+    base, _ = _make("llama-tiny")
+    sizes = unit_numels(base.parts)
+    assert sizes == [u.total_size for u in base.transformer_layers]
+    budget = 12 * (sizes[0] + sizes[1]) + 100     # the embedding and the first decoder layer fit
+    auto, _ = _make("llama-tiny", state_device="auto", hbm_state_budget_gb=budget / 2 ** 30)
+    want = plan_state_placement(sizes, budget)
+    assert want[:2] == ["hbm", "hbm"] and "host" in want
+    assert [u.state_device for u in auto.transformer_layers] == want
+    for u in auto.transformer_layers:
+        assert u._params_flat.is_cuda == (u.state_device == "hbm")
+        assert auto.layer_optimizer.exp_avg_flat[u.layer_idx].is_cuda == (u.state_device == "hbm")
+    ids = _ids(base.config.vocab_size, 2, 32, 3, seed=13)
+    _train(base, ids)
+    _train(auto, ids)
+    for ub, ua in zip(base.transformer_layers, auto.transformer_layers):
+        assert np.array_equal(_bits(ub._params_flat.to(DEV)), _bits(ua._params_flat.to(DEV))), ub.layer_idx
+        assert np.array_equal(_bits(ub._bf16_flat), _bits(ua._bf16_flat))
+
+
+def test_timer_labels_and_stats(capsys):
+    """Every label of the reference's timer that has a counterpart here gets samples
+    (utils/timer.py:11-21), and print_layer_stats prints them in the reference's format."""
+    from slideformer_b200.model_compat import build_random_model
+    from slideformer_b200.offload_transformer import SlideFormerOffloader
+    model = build_random_model("llama-tiny", DEV, torch.bfloat16, seed=3)
+    eng = SlideFormerOffloader(model, DEV, torch.bfloat16, enable_timing=True, optimizer_kwargs=dict(HP),
+                               auto_backward_in_forward=False, activation_offload="host", weight_window=True)
+    ids = _ids(eng.config.vocab_size, 2, 32, 2, seed=14)
+    _train(eng, ids)
+    stats = eng.layer_timings_ms()
+    n_units = len(eng.transformer_layers)
+    for op in ("forward", "backward", "parameter_update", "h2d_transfer_fw", "h2d_transfer_bw", "ac_fwd_d2h", "ac_bwd_h2d"):
+        assert op in stats and all(ms >= 0 for _, ms, _ in stats[op]), op
+    assert len(stats["forward"]) == n_units and len(stats["parameter_update"]) == n_units
+    assert eng.parameter_update_ms().keys() == set(range(n_units))
+    eng.print_layer_stats()
+    eng.print_layer_stats(show_history=True)
+    eng.print_layer_stats(layer_idx=1)
+    text = capsys.readouterr().out
+    for label in ("Current Step Layer Statistics:", "Historical Average Layer Statistics:", "  forward: ", "  backward: ",
+                  "  parameter update: ", "  h2d transfer fw: ", "  ac fwd d2h: ", "  ac bwd h2d: ", "avg across", "avg over"):
+        assert label in text, label
+
+
 def test_inference_forward_and_lr_update():
     eng, plain = _make("llama-tiny")
     ids = _ids(eng.config.vocab_size, 2, 16, 1)[0]

@@ -61,3 +61,17 @@ def test_grad_hooks_travel_in_the_scalars():
     assert lib.sf_set_push_tuning(5, -1) == _lib.SF_ERR_ARG
     assert lib.sf_set_push_tuning(-1, -1) == 0
     lib.sf_adam_destroy(oid)
+
+
+def test_state_placement_plan_and_timer_labels():
+    from slideformer_b200.offload_transformer import plan_state_placement
+    from slideformer_b200.transformer_layer import TIMING_LABELS, format_timing_label
+    assert plan_state_placement([10, 20, 30], 12 * 30) == ["hbm", "hbm", "host"]
+    assert plan_state_placement([10, 20, 30], 0) == ["host"] * 3
+    assert plan_state_placement([10, 20, 5], 12 * 15) == ["hbm", "host", "hbm"]   # later small units still fit
+    assert plan_state_placement([], 100) == []
+    # the nine labels of the reference's timer (utils/timer.py:11-21)
+    assert set(TIMING_LABELS.values()) == {"h2d transfer fw", "h2d transfer bw", "d2h transfer fw", "d2h transfer bw",
+                                           "forward", "backward", "parameter update", "ac fwd d2h", "ac bwd h2d"}
+    assert format_timing_label("parameter_update") == "parameter update"
+    assert format_timing_label("something_else") == "something else"
