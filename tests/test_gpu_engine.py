@@ -336,4 +336,4 @@ def test_layer_stats_and_csv(tmp_path, capsys):
     eng.print_layer_stats()
     eng.print_layer_stats(layer_idx=1, show_history=True)
     out = capsys.readouterr().out
-    assert "Current Step Layer Statistics" in out and "parameter update" in out and "layer 1" in out
+    assert "Current Step Layer Statistics" in out and "parameter update" in out and "Layer 1 Statistics" in out
