@@ -163,6 +163,27 @@ int sf_adam_step_sharded_push(const SfAdamScalars* s, float* p, const void* cons
                                uint16_t* const* peer_out, int world, int g_dtype, float* m, float* v,
                                uint64_t n, uint64_t vec_n, void* stream);
 
+/* Up to SF_MAX_SEGMENTS calls of sf_adam_step_sharded_push in ONE kernel launch, for models made
+ * of many small units (the reference makes one adam_update per unit and chunk,
+ * multi_gpu/transformer_layer.py:417-458; a launch and two cross-rank barriers per unit cost more
+ * than the update itself when a unit has a few million parameters).  Each segment keeps the
+ * constants of its own reference call, so the caller still calls sf_adam_scalars once per
+ * segment, in the reference's order, and the results are bit-identical to separate launches.
+ * world <= 8; segments with n == 0 are skipped; all segments must share the decay mode and the
+ * gradient hooks.  peer_g / peer_out: `world` pointers each, as in sf_adam_step_sharded_push. */
+#define SF_MAX_SEGMENTS 32
+typedef struct SfPushSegment {
+    SfAdamScalars s;
+    float* p;
+    float* m;
+    float* v;
+    const void* const* peer_g;
+    uint16_t* const* peer_out;
+    uint64_t n;
+    uint64_t vec_n;
+} SfPushSegment;
+int sf_adam_step_sharded_push_multi(const SfPushSegment* segs, int nseg, int world, int g_dtype, void* stream);
+
 /* No counterpart in the reference: sf_adam_step_sharded_push with the exchange done inside the
  * NVSwitch (NVLS).  mc_g / mc_out are MULTICAST device addresses (cuMulticast* objects bound to
  * the same offset of every rank's bf16 gradient buffer / bf16 layer buffer) at this slice;

@@ -37,6 +37,15 @@ class SfAdamScalars(C.Structure):
         return tuple(getattr(self, k) for k, _ in self._fields_)
 
 
+SF_MAX_SEGMENTS = 32
+
+
+class SfPushSegment(C.Structure):
+    _fields_ = [("s", SfAdamScalars), ("p", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
+                ("peer_g", C.POINTER(C.c_void_p)), ("peer_out", C.POINTER(C.c_void_p)),
+                ("n", C.c_uint64), ("vec_n", C.c_uint64)]
+
+
 class SfError(RuntimeError):
     """A C-ABI call returned a non-zero status."""
 
@@ -58,6 +67,7 @@ SIGNATURES = {
                                   _u64, _u64, _vp]),
     "sf_adam_step_sharded_push": (_i, [C.POINTER(SfAdamScalars), _vp, C.POINTER(_vp), C.POINTER(_vp), _i, _i, _vp, _vp,
                                        _u64, _u64, _vp]),
+    "sf_adam_step_sharded_push_multi": (_i, [C.POINTER(SfPushSegment), _i, _i, _i, _vp]),
     "sf_adam_step_sharded_nvls": (_i, [C.POINTER(SfAdamScalars), _vp, _vp, _vp, C.POINTER(_vp), C.POINTER(_vp), _i, _vp, _vp,
                                        _u64, _u64, _vp]),
     "sf_dp_mean": (_i, [C.POINTER(_vp), _i, _i, _vp, _u64, _vp]),

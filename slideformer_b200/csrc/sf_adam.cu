@@ -461,6 +461,64 @@ int sf_adam_step_sharded_push(const SfAdamScalars* s, float* p, const void* cons
     return launch_push(x, p, peer_g, peer_out, world, g_dtype, m, v, n, vec_n, a16, (cudaStream_t)stream);
 }
 
+int sf_adam_step_sharded_push_multi(const SfPushSegment* segs, int nseg, int world, int g_dtype, void* stream)
+{
+    if (g_dtype != SF_GRAD_BF16 && g_dtype != SF_GRAD_F32)
+        return fail(SF_ERR_DTYPE, "gradient dtype code " + std::to_string(g_dtype) + " is not supported (0 = bf16, 1 = fp32)");
+    if (world < 1 || world > SF_MULTI_MAX_WORLD)
+        return fail(SF_ERR_ARG, "world must be in [1, " + std::to_string(SF_MULTI_MAX_WORLD) + "] for the multi-segment launch");
+    if (nseg < 0 || nseg > SF_MULTI_MAX_SEGMENTS)
+        return fail(SF_ERR_ARG, "nseg must be in [0, " + std::to_string(SF_MULTI_MAX_SEGMENTS) + "]");
+    if (nseg == 0) return SF_OK;
+    if (!segs) return fail(SF_ERR_NULL, "segs is NULL");
+    SegTable table;
+    table.nseg = 0;
+    table.world = world;
+    table.fworld = (float)world;
+    int mode = -1;
+    bool ex = false;
+    SfGradStats* stats = nullptr;
+    uint64_t ctas = 0;
+    for (int k = 0; k < nseg; k++) {
+        const SfPushSegment& sg = segs[k];
+        bool a16 = false;
+        if (int rc = check_peers(&sg.s, sg.p, sg.peer_g, sg.peer_out, true, world, g_dtype, sg.m, sg.v, nullptr, sg.n, &a16))
+            return rc;
+        if (sg.n == 0) continue;
+        StepCtx x;
+        make_ctx(&sg.s, &x);
+        if (mode < 0) {
+            mode = x.mode;
+            ex = x.ex;
+            stats = x.stats;
+        } else if (mode != x.mode || ex != x.ex || stats != x.stats) {
+            return fail(SF_ERR_ARG, "all segments of one launch must share the decay mode and the gradient hooks");
+        }
+        SegDev& d = table.seg[table.nseg++];
+        d.c = x.c;
+        d.p = sg.p;
+        d.m = sg.m;
+        d.v = sg.v;
+        for (int r = 0; r < SF_MULTI_MAX_WORLD; r++) {
+            d.g[r] = sg.peer_g[r < world ? r : 0];
+            d.o[r] = sg.peer_out[r < world ? r : 0];
+        }
+        d.n = sg.n;
+        d.vec_n = sg.vec_n < sg.n ? sg.vec_n : sg.n;
+        d.nvec = a16 ? (d.vec_n & ~(uint64_t)3) : 0;
+        uint64_t c = (d.nvec + 1023) / 1024;
+        const uint64_t rem = (d.n - d.nvec + 255) / 256;
+        if (c < (rem < 1024 ? rem : 1024)) c = rem < 1024 ? rem : 1024;
+        if (c < 1) c = 1;
+        d.first_cta = (uint32_t)ctas;
+        d.num_ctas = (uint32_t)c;
+        ctas += c;
+        if (ctas > 0x7fffffffull) return fail(SF_ERR_SIZE, "too many elements for one multi-segment launch");
+    }
+    if (table.nseg == 0) return SF_OK;
+    return launch_push_multi(table, (int)ctas, mode, ex, stats, g_dtype, (cudaStream_t)stream);
+}
+
 int sf_adam_step_sharded_nvls(const SfAdamScalars* s, float* p, const void* mc_g, uint16_t* mc_out,
                                const void* const* peer_g, uint16_t* const* peer_out, int world, float* m,
                                float* v, uint64_t n, uint64_t vec_n, void* stream)

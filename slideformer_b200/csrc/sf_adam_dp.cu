@@ -164,6 +164,20 @@ int launch_push(const StepCtx& x, float* p, const void* const* peer_g, uint16_t*
     return push_any<float, 0, 4>(x, p, peer_g, peer_out, world, m, v, n, vec_n, a16, st);
 }
 
+int launch_push_multi(const SegTable& table, int total_ctas, int mode, bool ex, SfGradStats* stats, int g_dtype,
+                      cudaStream_t st)
+{
+    return dispatch_mode_ex(mode, ex, [&](auto MODE, auto EX) -> int {
+        constexpr int M = decltype(MODE)::value;
+        constexpr bool E = decltype(EX)::value;
+        if (g_dtype == SF_GRAD_BF16)
+            adam_push_multi_kernel<uint16_t, M, E><<<total_ctas, 256, 0, st>>>(table, stats);
+        else
+            adam_push_multi_kernel<float, M, E><<<total_ctas, 256, 0, st>>>(table, stats);
+        return check_launch("adam_push_multi_kernel");
+    });
+}
+
 int launch_nvls(const StepCtx& x, float* p, const void* mc_g, uint16_t* mc_out, const void* const* peer_g,
                 uint16_t* const* peer_out, int world, float* m, float* v, uint64_t n, uint64_t vec_n,
                 cudaStream_t st)

@@ -64,6 +64,8 @@ int launch_sharded(const StepCtx& x, float* p, const void* const* peer_g, int wo
                    float* v, uint16_t* out, uint64_t n, uint64_t vec_n, bool a16, cudaStream_t st);
 int launch_push(const StepCtx& x, float* p, const void* const* peer_g, uint16_t* const* peer_out, int world,
                 int g_dtype, float* m, float* v, uint64_t n, uint64_t vec_n, bool a16, cudaStream_t st);
+int launch_push_multi(const sfk::SegTable& table, int total_ctas, int mode, bool ex, SfGradStats* stats, int g_dtype,
+                      cudaStream_t st);
 int launch_nvls(const StepCtx& x, float* p, const void* mc_g, uint16_t* mc_out, const void* const* peer_g,
                 uint16_t* const* peer_out, int world, float* m, float* v, uint64_t n, uint64_t vec_n,
                 cudaStream_t st);

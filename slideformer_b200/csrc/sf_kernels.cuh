@@ -591,6 +591,104 @@ adam_push_kernel(K c, float* __restrict__ p, GradPeers<ELT, W> gs, float* __rest
     if (EX) stat_flush<256>(acc, stats);
 }
 
+// Many small slices in ONE launch of the pull + push step: a model made of small units (GPT-2
+// small: 14 units of 2 to 39 M parameters) otherwise pays one launch and two cross-rank stream
+// barriers per unit.  Every segment carries the constants of its own reference call (the host
+// state machine still advances once per call), its own arrays and its own peer pointers; a
+// CTA finds its segment from the table in the kernel parameters.  4 elements per thread.
+#define SF_MULTI_MAX_SEGMENTS 32
+#define SF_MULTI_MAX_WORLD 8
+struct SegDev {
+    K c;
+    float* p;
+    float* m;
+    float* v;
+    const void* g[SF_MULTI_MAX_WORLD];
+    uint16_t* o[SF_MULTI_MAX_WORLD];
+    uint64_t nvec, n, vec_n;
+    uint32_t first_cta, num_ctas;
+};
+struct SegTable {
+    int nseg, world;
+    float fworld;
+    SegDev seg[SF_MULTI_MAX_SEGMENTS];
+};
+
+template <typename ELT>
+__device__ __forceinline__ void seg_load4(const SegDev& d, int world, float fworld, uint64_t i, float (&o)[4])
+{
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int r = 0; r < world; r++) {
+        float t[4];
+        if (sizeof(ELT) == 2) {
+            unpack4(ld2u<1>(reinterpret_cast<const uint16_t*>(d.g[r]) + i), t);
+        } else {
+            float4 q = ld4<1>(reinterpret_cast<const float*>(d.g[r]) + i);
+            t[0] = q.x; t[1] = q.y; t[2] = q.z; t[3] = q.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) acc[k] = __fadd_rn(acc[k], t[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) o[k] = __fdiv_rn(acc[k], fworld);
+}
+
+template <typename ELT>
+__device__ __forceinline__ float seg_load1(const SegDev& d, int world, float fworld, uint64_t i)
+{
+    float acc = 0.f;
+    for (int r = 0; r < world; r++) {
+        float t;
+        if (sizeof(ELT) == 2) t = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(d.g[r])[i]);
+        else t = reinterpret_cast<const float*>(d.g[r])[i];
+        acc = __fadd_rn(acc, t);
+    }
+    return __fdiv_rn(acc, fworld);
+}
+
+template <typename ELT, int MODE, bool EX>
+__global__ void __launch_bounds__(256, 5)
+adam_push_multi_kernel(const __grid_constant__ SegTable t, SfGradStats* stats)
+{
+    int s = 0;
+    while (s + 1 < t.nseg && blockIdx.x >= t.seg[s + 1].first_cta) s++;
+    const SegDev& d = t.seg[s];
+    const uint64_t cta = blockIdx.x - d.first_cta;
+    StatAcc acc{0.f, 0u};
+    const uint64_t i = (cta * 256 + threadIdx.x) * 4;
+    if (i < d.nvec) {
+        float G[4];
+        seg_load4<ELT>(d, t.world, t.fworld, i, G);
+        float4 P = ld4<1>(d.p + i), M = ld4<1>(d.m + i), V = ld4<1>(d.v + i);
+        if (EX) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) G[k] = grad_pre<EX>(d.c, G[k], acc);
+        }
+        adam_body<MODE>(d.c, P.x, G[0], M.x, V.x);
+        adam_body<MODE>(d.c, P.y, G[1], M.y, V.y);
+        adam_body<MODE>(d.c, P.z, G[2], M.z, V.z);
+        adam_body<MODE>(d.c, P.w, G[3], M.w, V.w);
+        st4<1>(d.p + i, P);
+        st4<1>(d.m + i, M);
+        st4<1>(d.v + i, V);
+        uint2 o;
+        o.x = pack_bf16x2(P.x, P.y);
+        o.y = pack_bf16x2(P.z, P.w);
+        for (int r = 0; r < t.world; r++) *reinterpret_cast<uint2*>(d.o[r] + i) = o;
+    }
+    for (uint64_t j = d.nvec + cta * 256 + threadIdx.x; j < d.n; j += (uint64_t)d.num_ctas * 256) {
+        float pp = d.p[j], mm = d.m[j], vv = d.v[j];
+        float g = grad_pre<EX>(d.c, seg_load1<ELT>(d, t.world, t.fworld, j), acc);
+        if (j < d.vec_n) adam_body<MODE>(d.c, pp, g, mm, vv);
+        else adam_tail<MODE>(d.c, pp, g, mm, vv);
+        d.p[j] = pp; d.m[j] = mm; d.v[j] = vv;
+        const uint16_t ob = (uint16_t)f32_to_bf16_bits(pp);
+        for (int r = 0; r < t.world; r++) d.o[r][j] = ob;
+    }
+    if (EX) stat_flush<256>(acc, stats);
+}
+
 // The same step with the exchange done by the NVSwitch (NVLS): `mc_g` and `mc_out` are MULTICAST
 // addresses that alias the same offset of every rank's gradient buffer / bf16 layer buffer.
 //   multimem.ld_reduce  one 16-byte request returns the sum of all ranks' 8 bf16 gradients, added

@@ -81,7 +81,8 @@ class SlideFormerOffloader(nn.Module):
                  auto_backward_in_forward: bool = True, shared_dp=None, *, state_device: str = "hbm",
                  activation_offload: str = "hbm", activation_checkpoint: bool = True, loss_chunk_tokens: int = 4096,
                  update_chunk: Optional[int] = None, weight_window: bool = False,
-                 hbm_state_budget_gb: Optional[float] = None, enable_nvtx: bool = True):
+                 hbm_state_budget_gb: Optional[float] = None, enable_nvtx: bool = True,
+                 batch_small_units: Optional[bool] = None):
         super().__init__()
         if not isinstance(device, torch.device):
             raise TypeError("device must be torch.device")
@@ -121,7 +122,23 @@ class SlideFormerOffloader(nn.Module):
             self.opt_stream = torch.cuda.Stream()
         n_units = min(3 if double_buffer else 2, len(self.decoder_layers) + 2)
         self.gpu_unit_size = n_units
+        # Small models under data parallelism: every unit keeps its own exchange slot and all units
+        # are updated by ONE multi-segment launch (one barrier pair) after backward, instead of one
+        # launch and two cross-rank barriers per unit, which cost more than the update itself when
+        # a unit has a few million parameters.  Default: on when the per-unit slots fit in 2 GiB.
+        all_units = len(self.decoder_layers) + 2
+        slots_bytes = all_units * self.max_param_size * 2
+        can_batch = (shared_dp is not None and not weight_window and shared_dp.push_weights and not shared_dp.nvls
+                     and shared_dp.world_size <= 8 and shared_dp.dtype == torch.bfloat16)
+        if batch_small_units is None:
+            batch_small_units = can_batch and slots_bytes <= (2 << 30) and shared_dp._cap == 0
+        elif batch_small_units and not can_batch:
+            raise ValueError("batch_small_units needs shared_dp in push mode with resident bf16 weights and at most 8 ranks")
+        self.batch_small_units = bool(batch_small_units)
+        self._deferred = []
         if shared_dp is not None:
+            if self.batch_small_units:
+                shared_dp.ensure_exchange_slots(all_units)
             if shared_dp.exchange_slots < n_units:
                 raise ValueError(f"shared_dp needs at least {n_units} exchange slots")
             shared_dp.reserve_exchange(self.max_param_size)
@@ -174,6 +191,12 @@ class SlideFormerOffloader(nn.Module):
         self._grad_pool = GradUnitPool(n_units, self.max_param_size, dtype, device, buffers)
         for u in self.transformer_layers:
             u.grad_pool = self._grad_pool
+        if self.batch_small_units:
+            for j, u in enumerate(self.transformer_layers):
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(device))
+                u.own_grad_unit = {"grad": shared_dp.grad_buffer(j), "reuse_ready": ev, "slot": j}
+                u.defer_to = self._deferred
 
         self.activation_store = None
         self._activation_layout_signature = None
@@ -221,8 +244,41 @@ class SlideFormerOffloader(nn.Module):
         stream wait for the optimizer stream, and synchronise (offload_transformer.py:326-335)."""
         for unit in self.transformer_layers:
             unit.flush()
+        self._update_deferred_units()
         torch.cuda.current_stream(self.device).wait_stream(self.opt_stream)
         torch.cuda.synchronize(self.device)
+
+    def _update_deferred_units(self):
+        """Batched small-unit mode: one multi-segment update of every unit whose backward finished,
+        in the order they finished (the order the reference updates them), on the optimizer stream."""
+        if not self._deferred:
+            return
+        import time as _time
+        h0 = _time.perf_counter()
+        opt, dp, s = self.layer_optimizer, self.shared_dp, self.opt_stream
+        pending, self._deferred[:] = list(self._deferred), []
+        items = []
+        with torch.cuda.stream(s):
+            for u, unit in pending:
+                s.wait_event(u.compute_ready_bw)
+                if u._dp_group is None:
+                    u._dp_group = dict(opt.defaults, step=0)
+                u._dp_group["step"] += 1
+                u._dp_group["lr"] = opt.defaults["lr"]
+                u._dp_state.step = u._dp_group["step"]
+                for cs in range(0, u.total_size, u.update_chunk):
+                    items.append((u.layer_idx, u._dp_group, cs, min(cs + u.update_chunk, u.total_size), unit["slot"]))
+            from .transformer_layer import _Span
+            span = _Span(pending[0][0], "parameter_update", "Update_All_Layers", s)
+            dp.fused_update_multi(items, opt)
+            span.close()
+            for u, unit in pending:
+                u.update_done.record(s)
+                unit["reuse_ready"].record(s)
+                u._update_recorded = True
+                for _, p in u._managed_named_params:
+                    p.grad = None
+        pending[0][0].host_update_seconds += _time.perf_counter() - h0
 
     def _ensure_activation_storage(self, batch_size, seq_length, hidden_size):
         if self.activation_offload != "host":

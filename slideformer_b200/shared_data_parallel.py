@@ -230,6 +230,14 @@ class SharedDataParallel:
         self._peer_base = []
         self._base = None
 
+    def ensure_exchange_slots(self, slots: int):
+        """Collective: have at least `slots` exchange slots.  Only before any slot exists."""
+        if slots <= self.exchange_slots:
+            return
+        if self._cap or self._views_out:
+            raise RuntimeError("the number of exchange slots can only grow before the first layer is registered")
+        self.exchange_slots = int(slots)
+
     def reserve_exchange(self, elems: int):
         """Collective: make every exchange slot at least `elems` elements long.  Call it with the
         largest layer size before handing out `grad_buffer()` views: growing the slots later
@@ -376,12 +384,18 @@ class SharedDataParallel:
         overwritten (stream-ordered)."""
         self.raise_if_failed()
         state = self.layers[layer_idx]
-        self._validate(state, start, end, local_grad)
-        self._stage(slot, start, end, local_grad)
-        self.stream_barrier()
-        a, b = max(start, state.start), min(end, state.end)
         failure = None
         try:
+            self._validate(state, start, end, local_grad)
+            self._stage(slot, start, end, local_grad)
+        except Exception as exc:   # reported to every rank below, after the barrier this rank still owes
+            failure = exc
+        invalid = failure
+        self.stream_barrier()
+        a, b = max(start, state.start), min(end, state.end)
+        try:
+            if failure is not None:
+                raise failure
             k = max(b - a, 0)
             if self._mean is None or self._mean.numel() < k:
                 self._mean = torch.empty(max(k, min(self.chunk_numel, state.shard)), dtype=torch.float32,
@@ -396,9 +410,15 @@ class SharedDataParallel:
         except Exception as exc:  # propagate to every rank below
             failure = exc
         if check_errors and self.ctl.any_failed(failure is not None):
+            self.stream_barrier()
+            if invalid is not None:
+                raise invalid      # this rank's own bad arguments keep their type (ValueError), as in the reference
             self.error = failure if failure is not None else RuntimeError("a peer rank failed")
             self.raise_if_failed()
         elif failure is not None:
+            self.stream_barrier()
+            if invalid is not None:
+                raise invalid
             self.error = failure
             self.raise_if_failed()
         self.stream_barrier()
@@ -407,24 +427,106 @@ class SharedDataParallel:
     @torch.no_grad()
     def fused_update(self, layer_idx, adam, param_group: dict, start: int = 0, end: Optional[int] = None,
                      local_grad: Optional[torch.Tensor] = None, slot: int = 0, gather: bool = True,
-                     barrier: bool = True):
+                     barrier: bool = True, check_errors: bool = False):
         """Mean + Adam + bf16 cast in one kernel on this rank's part of [start, end), then (by
         default) the all-gather of the layer's bf16 weights.  `adam` is a LayerAdam (its scalar
         state machine advances once per call, like one reference adam_update).  barrier=False
         skips the leading cross-rank stream barrier: correct for the second and later chunks of
-        a layer whose whole gradient was complete on every rank before the first chunk's barrier."""
+        a layer whose whole gradient was complete on every rank before the first chunk's barrier.
+
+        A host-side failure on this rank between the two barriers (a rejected argument, a CUDA
+        error at launch) still enqueues the trailing barrier before it is raised, so the peers'
+        streams are not left waiting for this rank inside the current unit.  check_errors=True
+        additionally exchanges a failure flag over the host control plane (one gloo all-reduce
+        per call, which synchronises the hosts) and raises on EVERY rank, like `reduce_chunk`."""
         self.raise_if_failed()
         state = self.layers[layer_idx]
         end = state.numel if end is None else end
         if state.numel == 0:
             return
-        if not 0 <= start < end <= state.numel:
-            raise ValueError("Invalid gradient chunk")
-        if local_grad is not None:
-            self._validate(state, start, end, local_grad)
-            self._stage(slot, start, end, local_grad)
+        failure = None
+        try:
+            if not 0 <= start < end <= state.numel:
+                raise ValueError("Invalid gradient chunk")
+            if local_grad is not None:
+                self._validate(state, start, end, local_grad)
+                self._stage(slot, start, end, local_grad)
+        except Exception as exc:
+            failure = exc
+        invalid = failure
         if barrier:
             self.stream_barrier()
+        if failure is None:
+            try:
+                self._launch_fused(state, adam, param_group, start, end, slot)
+            except Exception as exc:
+                failure = exc
+        if (check_errors and self.ctl.any_failed(failure is not None)) or failure is not None:
+            self.all_gather_params(layer_idx)      # keep the barrier count of this unit balanced
+            if invalid is not None:
+                raise invalid      # this rank's own bad arguments keep their type (ValueError)
+            self.error = failure if failure is not None else RuntimeError("a peer rank failed")
+            self.raise_if_failed()
+        if gather:
+            self.all_gather_params(layer_idx)
+
+    @torch.no_grad()
+    def fused_update_multi(self, items, adam):
+        """`fused_update` for many (layer, chunk) pieces with ONE barrier before, one or a few kernel
+        launches (up to 32 pieces each) and ONE barrier after, instead of a launch and two barriers
+        per piece: what a model made of small units needs.  items: sequence of
+        (layer_idx, param_group, start, end, slot) in the order the reference would update them;
+        every piece is still one reference adam_update (the scalar state machine advances once per
+        piece on every rank), so the bits equal those of separate `fused_update` calls.  The
+        whole gradient of every listed layer must be complete in its exchange slot on every rank
+        before this call is enqueued.  Push mode only (resident bf16 layers, at most 8 ranks)."""
+        self.raise_if_failed()
+        if self.world_size > 8:
+            raise ValueError("fused_update_multi supports at most 8 ranks")
+        segs, keep = [], []
+        for layer_idx, param_group, start, end, slot in items:
+            state = self.layers[layer_idx]
+            if state.numel == 0:
+                continue
+            if state.peer_bf16 is None or state.mc_bf16:
+                raise ValueError("fused_update_multi needs push-mode layers (resident, peer-mapped bf16 weights)")
+            end = state.numel if end is None else end
+            if not 0 <= start < end <= state.numel:
+                raise ValueError("Invalid gradient chunk")
+            sg = _lib.SfPushSegment()
+            _lib.check(self._lib.sf_adam_scalars(adam.optimizer_id, int(param_group["step"]), param_group["lr"],
+                                                 param_group["betas"][0], param_group["betas"][1], param_group["eps"],
+                                                 param_group["weight_decay"], int(param_group["bias_correction"] == 1),
+                                                 C.byref(sg.s)))
+            a, b = max(start, state.start), min(end, state.end)
+            if b <= a:
+                continue                        # nothing of this piece is ours; the state machine still advanced
+            k, lo = b - a, a - state.start
+            pg, po = self._peer_ptrs(slot, a), self._push_ptrs(state, a)
+            keep += [pg, po]
+            sg.p = state.params[lo:lo + k].data_ptr()
+            sg.m = state.exp_avg[lo:lo + k].data_ptr()
+            sg.v = state.exp_avg_sq[lo:lo + k].data_ptr()
+            sg.peer_g, sg.peer_out = pg, po
+            sg.n, sg.vec_n = k, slice_vec_n(start, end, a, b)
+            segs.append(sg)
+        self.stream_barrier()
+        failure = None
+        try:
+            with torch.cuda.device(self.device):
+                stream = torch.cuda.current_stream().cuda_stream
+                for i in range(0, len(segs), _lib.SF_MAX_SEGMENTS):
+                    part = segs[i:i + _lib.SF_MAX_SEGMENTS]
+                    arr = (_lib.SfPushSegment * len(part))(*part)
+                    _lib.check(self._lib.sf_adam_step_sharded_push_multi(arr, len(part), self.world_size, self._gcode, stream))
+        except Exception as exc:
+            failure = exc
+        self.stream_barrier()                   # all pushes landed everywhere; gradients may be overwritten
+        if failure is not None:
+            self.error = failure
+            self.raise_if_failed()
+
+    def _launch_fused(self, state, adam, param_group, start, end, slot):
         sc = _lib.SfAdamScalars()
         _lib.check(self._lib.sf_adam_scalars(adam.optimizer_id, int(param_group["step"]), param_group["lr"],
                                              param_group["betas"][0], param_group["betas"][1], param_group["eps"],
@@ -459,8 +561,6 @@ class SharedDataParallel:
                         C.byref(sc), state.params[lo:lo + k].data_ptr(), self._peer_ptrs(slot, a), self.world_size,
                         self._gcode, state.exp_avg[lo:lo + k].data_ptr(), state.exp_avg_sq[lo:lo + k].data_ptr(),
                         state.bf16[a:b].data_ptr(), k, vec_local, stream))
-        if gather:
-            self.all_gather_params(layer_idx)
 
     @torch.no_grad()
     def all_gather_params(self, layer_idx, async_op: bool = False, force_nccl: bool = False):

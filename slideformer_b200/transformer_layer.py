@@ -179,6 +179,8 @@ class OffloadLayerWrapper(nn.Module):
         self.timings: Dict[str, List] = {"parameter_update": []}
         self.host_update_seconds = 0.0   # host time spent enqueueing optimizer steps (not device time)
 
+        self.own_grad_unit = None    # batched small-unit mode: this unit's private exchange slot
+        self.defer_to = None         # batched small-unit mode: list the engine drains after backward
         self.weight_pool = weight_pool
         self.comm_stream = comm_stream
         self.weights_ready = torch.cuda.Event()
@@ -282,7 +284,7 @@ class OffloadLayerWrapper(nn.Module):
             self._acquire_weights(is_bwd if bwd_phase is None else bwd_phase)
         if not is_bwd or self._unit is not None:
             return
-        unit = self.grad_pool.get()
+        unit = self.own_grad_unit if self.own_grad_unit is not None else self.grad_pool.get()
         cur = torch.cuda.current_stream(self.device)
         cur.wait_event(unit["reuse_ready"])
         g = unit["grad"]
@@ -379,6 +381,11 @@ class OffloadLayerWrapper(nn.Module):
     # ---- the optimizer step ----------------------------------------------------------------------
     def update_params(self):
         """Enqueue this unit's Adam step on the optimizer stream, behind `compute_ready_bw`."""
+        if self._unit is not None and self.defer_to is not None:
+            # batched small-unit mode: the engine updates all units in one launch after backward
+            self.defer_to.append((self, self._unit))
+            self._unit = None
+            return None
         unit, self._unit = self._unit, None
         if unit is None:
             return None

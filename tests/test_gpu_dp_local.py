@@ -292,3 +292,64 @@ def test_shared_data_parallel_slices_cover_a_layer(oracle, lib):
             case.check(f"step {step}")
     finally:
         case.close(lib)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_multi_segment_launch_equals_separate_reference_calls(world, dtype, oracle, lib):
+    """sf_adam_step_sharded_push_multi: segments of very different sizes (one empty, one misaligned
+    by an element, one whose tail arithmetic starts early) in ONE launch.  Each segment is its own
+    reference call on a shared optimizer object, so the calls after the first of a step take the
+    pow() branch of the scalar state machine; the oracle follows the same sequence."""
+    from slideformer_b200 import _lib
+    sizes = [70_001, 0, 16 * 9 + 5, 1024 * 300, 7, 2048 * 11 + 1]
+    offs = [0, 0, 0, 0, 0, 1]
+    gcode = _lib.SF_GRAD_BF16 if dtype == torch.bfloat16 else _lib.SF_GRAD_F32
+    esize = 2 if dtype == torch.bfloat16 else 4
+    oid = 551000 + world
+    _lib.check(lib.sf_adam_create(oid, *CFG0, 1, 0))
+    orc = oracle.OracleAdam(*CFG0, True)
+    gen = torch.Generator().manual_seed(world)
+    cpu, devs = [], []
+    for n, off in zip(sizes, offs):
+        p0 = torch.randn(n, generator=gen) * 0.02
+        cpu.append([p0.numpy().copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.uint16)])
+        devs.append(dict(p=torch.cat([torch.zeros(off), p0]).to(DEV), m=torch.zeros(n + off, device=DEV),
+                         v=torch.zeros(n + off, device=DEV),
+                         outs=[torch.zeros(n + off, device=DEV, dtype=torch.bfloat16) for _ in range(world)]))
+    try:
+        for step in (1, 2, 3):
+            segs = (_lib.SfPushSegment * len(sizes))()
+            keep = []
+            for k, (n, off) in enumerate(zip(sizes, offs)):
+                rows = _rows(world, n, dtype, gen)
+                gd = [torch.cat([torch.zeros(off, dtype=dtype), rows[r]]).to(DEV) for r in range(world)]
+                vec_n = 16 if k == 3 else n & ~15
+                if n:
+                    mean = oracle.rank_mean(np.ascontiguousarray(_np(rows)))
+                else:
+                    mean = np.zeros(0, np.float32)
+                p, m, v, o = cpu[k]
+                orc.adam_update(step, *CFG0, True, p, mean, m, v, o, vec_n=vec_n)
+                _lib.check(lib.sf_adam_scalars(oid, step, *CFG0, 1, C.byref(segs[k].s)))
+                d = devs[k]
+                pg = (C.c_void_p * world)(*[t.data_ptr() + off * esize for t in gd])
+                po = (C.c_void_p * world)(*[t.data_ptr() + off * 2 for t in d["outs"]])
+                keep += [gd, pg, po]
+                segs[k].p, segs[k].m, segs[k].v = (d[x].data_ptr() + 4 * off for x in "pmv")
+                segs[k].peer_g, segs[k].peer_out = pg, po
+                segs[k].n, segs[k].vec_n = n, vec_n
+            before = lib.sf_launch_count()
+            _lib.check(lib.sf_adam_step_sharded_push_multi(segs, len(sizes), world, gcode, torch.cuda.current_stream().cuda_stream))
+            assert lib.sf_launch_count() == before + 1
+            torch.cuda.synchronize()
+            for k, (n, off) in enumerate(zip(sizes, offs)):
+                p, m, v, o = cpu[k]
+                d = devs[k]
+                assert np.array_equal(_bits32(d["p"][off:]), p.view(np.uint32)), (step, k, "p")
+                assert np.array_equal(_bits32(d["m"][off:]), m.view(np.uint32)), (step, k, "m")
+                assert np.array_equal(_bits32(d["v"][off:]), v.view(np.uint32)), (step, k, "v")
+                for out in d["outs"]:
+                    assert np.array_equal(_bits16(out[off:]), o), (step, k, "bf16")
+    finally:
+        lib.sf_adam_destroy(oid)

@@ -61,7 +61,9 @@ def _worker(rank, world, path, mode):
         init_full = {}
         eng = SlideFormerOffloader(model, dev, torch.bfloat16, enable_timing=False, enable_memory_stats=False,
                                    optimizer_kwargs=dict(HP), auto_backward_in_forward=False, shared_dp=dp,
-                                   weight_window=(mode == "window"))
+                                   weight_window=(mode == "window"), update_chunk=(8192 if mode == "resident_chunked" else None),
+                                   batch_small_units=(False if mode == "resident_per_unit" else None))
+        assert eng.batch_small_units == (mode in ("resident", "resident_chunked"))
         units = eng.transformer_layers
         # expected state, full layers, kept on every rank
         exp = {}
@@ -118,9 +120,11 @@ def _worker(rank, world, path, mode):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["resident", "window", "meta"])
+@pytest.mark.parametrize("mode", ["resident", "resident_chunked", "resident_per_unit", "window", "meta"])
 def test_sharded_engine_two_ranks(mode):
-    """resident: every rank keeps all bf16 layers (weights pushed by the update kernel);
+    """resident: every rank keeps all bf16 layers (weights pushed by the update kernel), all units
+    updated by one multi-segment launch after backward; resident_chunked: the same with units cut
+    into several reference calls; resident_per_unit: one launch and barrier pair per unit;
     window: only bf16 slices are kept and layers are all-gathered into window units on demand;
     meta: window mode on a model whose weights are created per unit (never whole on one GPU)."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:

@@ -249,6 +249,19 @@ def _worker(rank, world, path, scenario):
             with pytest.raises(ValueError, match="Invalid gradient chunk"):
                 dp.error = None
                 dp.reduce_chunk(0, 0, 65, torch.zeros(65, dtype=torch.bfloat16, device=dev), update)
+            # bad arguments on ONE rank: that rank gets its ValueError, the other learns of it on the
+            # host, and both have enqueued the same number of stream barriers (nothing hangs)
+            adam = LayerAdam(lr=1e-3)
+            try:
+                dp.fused_update(0, adam, dict(adam.defaults, step=1), 0, 65 if rank == 1 else 64, check_errors=True)
+                outcome = "ok"
+            except ValueError:
+                outcome = "value"
+            except RuntimeError as exc:
+                outcome = "runtime" if "distributed update failed" in str(exc) else "other"
+            assert outcome == ("value" if rank == 1 else "runtime"), (rank, outcome)
+            dp.error = None
+            dp.fused_update(0, adam, dict(adam.defaults, step=2), 0, 64, check_errors=True)   # and the next call works
             torch.cuda.synchronize()
         elif scenario == "mismatch":
             dp = SharedDataParallel(chunk_numel=64, dtype=torch.bfloat16, timeout_seconds=60)
