@@ -637,6 +637,11 @@ def main_b200(args):
 
     sampler = ClockSampler(local)
     sampler.start()
+    from slideformer_b200.numa import gpu_numa_cpus
+    near = gpu_numa_cpus(dev)
+    host_info = {"usable_cpus": cpu_threads(),
+                 "pinned_buffers": (f"allocated from the {len(near)} CPUs of the GPU's NUMA node" if near
+                                    else "allocated where the process runs (the host exposes no NUMA node for the GPU)")}
 
     def barrier():
         if world > 1:
@@ -867,6 +872,7 @@ def main_b200(args):
                            "hyper": {"lr": HP["lr"], "betas": list(HP["betas"]), "eps": HP["eps"], "weight_decay": HP["weight_decay"]}},
                 "hbm_gbs": BYTES_PER_PARAM * value, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
                 "gpu_launches": int(launches), "clocks": sampler.summary()}
+        line["host"] = host_info
         line.update(extra)
         if finetune is not None:
             line["finetune"] = finetune
