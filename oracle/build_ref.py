@@ -24,7 +24,17 @@ import time
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-DEFAULT_REFERENCE = Path(os.environ.get("SLIDEFORMER_REFERENCE", "/root/reference"))
+
+
+def default_reference() -> Path | None:
+    """Where the reference checkout is: $SLIDEFORMER_REFERENCE, else a directory named `reference`
+    next to this repository; None when neither exists."""
+    env = os.environ.get("SLIDEFORMER_REFERENCE")
+    if env:
+        return Path(env)
+    sibling = HERE.parents[1] / "reference"
+    return sibling if sibling.is_dir() else None
+
 
 
 def ref_sources(reference: Path) -> list[Path]:
@@ -32,13 +42,15 @@ def ref_sources(reference: Path) -> list[Path]:
     return [csrc / "cpu_adam.cpp", csrc / "cpu_adam_impl.cpp"]
 
 
-def build(reference: Path = DEFAULT_REFERENCE, out_dir: Path = HERE / "_ref",
+def build(reference: Path | None = None, out_dir: Path = HERE / "_ref",
           march: str = "x86-64-v4", force: bool = False, verbose: bool = True) -> Path | None:
     """Compile the reference kernel.  Returns the .so path, or None if the sources are absent."""
-    srcs = ref_sources(reference)
-    if not all(s.exists() for s in srcs):
+    reference = Path(reference) if reference is not None else default_reference()
+    srcs = ref_sources(reference) if reference is not None else []
+    if not srcs or not all(s.exists() for s in srcs):
         if verbose:
-            print(f"[build_ref] reference sources not found under {reference}; keeping any prebuilt module")
+            print("[build_ref] reference sources not found (set SLIDEFORMER_REFERENCE to the checkout); "
+                  "keeping any prebuilt module")
         so = out_dir / "cpu_adam.so"
         return so if so.exists() else None
     out_dir.mkdir(parents=True, exist_ok=True)
@@ -104,7 +116,8 @@ def load(out_dir: Path = HERE / "_ref"):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", type=Path, default=DEFAULT_REFERENCE)
+    ap.add_argument("--reference", type=Path, default=None,
+                    help="reference checkout (default: $SLIDEFORMER_REFERENCE, else ../reference next to this repository)")
     ap.add_argument("--out", type=Path, default=HERE / "_ref")
     ap.add_argument("--march", default="x86-64-v4")
     ap.add_argument("--force", action="store_true")
