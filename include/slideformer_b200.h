@@ -290,6 +290,10 @@ int sf_set_tuning(int variant, int ctas_per_sm);
  * keep the current setting; the defaults are (8, 1).  For benchmarking; not thread safe. */
 int sf_set_push_tuning(int vec, int specialise_world);
 
+/* 8-element groups per thread of the NVLS kernel (sf_adam_step_sharded_nvls): 1, 2 or 4
+ * in-switch reductions in flight per thread.  For benchmarking; not thread safe. */
+int sf_set_nvls_tuning(int groups_per_thread);
+
 /* A plain copy kernel (16-byte loads and stores; dst, src and bytes multiples of 16) on device
  * pointers that may be local or peer-mapped.  It exists so that the NVLink traffic of the
  * data-parallel kernels can be compared with what a bare copy reaches between the same GPUs,

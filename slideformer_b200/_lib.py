@@ -81,6 +81,7 @@ SIGNATURES = {
     "sf_launch_count": (_u64, []),
     "sf_set_tuning": (_i, [_i, _i]),
     "sf_set_push_tuning": (_i, [_i, _i]),
+    "sf_set_nvls_tuning": (_i, [_i]),
     "sf_copy_bytes": (_i, [_vp, _vp, C.c_size_t, _vp]),
     "sf_dev_alloc": (_i, [C.c_size_t, C.POINTER(_vp)]),
     "sf_dev_free": (_i, [_vp]),

@@ -669,6 +669,14 @@ int sf_copy_bytes(void* dst, const void* src, size_t bytes, void* stream)
     return launch_copy16(dst, src, bytes / 16, (cudaStream_t)stream);
 }
 
+int sf_set_nvls_tuning(int groups_per_thread)
+{
+    if (groups_per_thread != 1 && groups_per_thread != 2 && groups_per_thread != 4)
+        return fail(SF_ERR_ARG, "groups_per_thread must be 1, 2 or 4");
+    g_tune.nvls_groups = groups_per_thread;
+    return SF_OK;
+}
+
 int sf_set_push_tuning(int vec, int specialise_world)
 {
     if (vec >= 0 && vec != 4 && vec != 8) return fail(SF_ERR_ARG, "vec must be 4 or 8 (or negative to keep the setting)");

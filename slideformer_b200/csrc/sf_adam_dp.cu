@@ -188,7 +188,9 @@ int launch_nvls(const StepCtx& x, float* p, const void* mc_g, uint16_t* mc_out, 
     auto dst = make_dst<0>(peer_out, world);
     const uint64_t body = vec_n < n ? vec_n : n;
     const uint64_t nvec = body & ~(uint64_t)7;
-    uint64_t ctas = (nvec + 2047) / 2048;
+    const int U = g_tune.nvls_groups;
+    const uint64_t tile = (uint64_t)2048 * U;
+    uint64_t ctas = (nvec + tile - 1) / tile;
     const uint64_t rem_ctas = (n - nvec + 255) / 256;
     const uint64_t rem_cap = (uint64_t)di.sms * 8;
     if (ctas < (rem_ctas < rem_cap ? rem_ctas : rem_cap)) ctas = rem_ctas < rem_cap ? rem_ctas : rem_cap;
@@ -196,7 +198,12 @@ int launch_nvls(const StepCtx& x, float* p, const void* mc_g, uint16_t* mc_out, 
     return dispatch_mode_ex(x.mode, x.ex, [&](auto MODE, auto EX) -> int {
         constexpr int M = decltype(MODE)::value;
         constexpr bool E = decltype(EX)::value;
-        adam_nvls_kernel<M, E><<<grid, 256, 0, st>>>(x.c, p, (const uint16_t*)mc_g, m, v, mc_out, gs, dst, nvec, n, vec_n, x.stats);
+        if (U == 1)
+            adam_nvls_kernel<M, E, 1><<<grid, 256, 0, st>>>(x.c, p, (const uint16_t*)mc_g, m, v, mc_out, gs, dst, nvec, n, vec_n, x.stats);
+        else if (U == 2)
+            adam_nvls_kernel<M, E, 2><<<grid, 256, 0, st>>>(x.c, p, (const uint16_t*)mc_g, m, v, mc_out, gs, dst, nvec, n, vec_n, x.stats);
+        else
+            adam_nvls_kernel<M, E, 4><<<grid, 256, 0, st>>>(x.c, p, (const uint16_t*)mc_g, m, v, mc_out, gs, dst, nvec, n, vec_n, x.stats);
         return check_launch("adam_nvls_kernel");
     });
 }

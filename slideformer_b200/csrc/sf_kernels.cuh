@@ -701,20 +701,33 @@ adam_push_multi_kernel(const __grid_constant__ SegTable t, SfGradStats* stats)
 // up to half a bf16 ulp of the sum: this kernel is NOT bit-exact and is offered beside the exact
 // adam_push_kernel, never in its place.  Elements [nvec, n) take the exact peer path.
 // The kernel waits on nothing; the caller orders it between two cross-rank stream barriers.
-template <int MODE, bool EX>
-__global__ void __launch_bounds__(256, 3)
+template <int MODE, bool EX, int U>
+__global__ void __launch_bounds__(256, U == 1 ? 4 : (U == 2 ? 3 : 2))
 adam_nvls_kernel(K c, float* __restrict__ p, const uint16_t* mc_g, float* __restrict__ m,
                  float* __restrict__ v, uint16_t* mc_out, GradPeers<uint16_t, 0> gs, OutPush<0> dst,
                  uint64_t nvec, uint64_t n, uint64_t vec_n, SfGradStats* stats)
 {
     StatAcc acc{0.f, 0u};
-    const uint64_t i = ((uint64_t)blockIdx.x * 256 + threadIdx.x) * 8;
-    if (i < nvec) {
-        uint4 q;
-        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-                     : "l"(mc_g + i)
-                     : "memory");
+    // U groups of 8 elements per thread, a tile of 2048 * U elements per CTA; all U in-switch
+    // reductions of a thread are requested before the first result is used
+    const uint64_t base = (uint64_t)blockIdx.x * (2048 * U) + (uint64_t)threadIdx.x * 8;
+    uint4 Q[U];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const uint64_t i = base + (uint64_t)u * 2048;
+        ok[u] = i < nvec;
+        if (ok[u])
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(Q[u].x), "=r"(Q[u].y), "=r"(Q[u].z), "=r"(Q[u].w)
+                         : "l"(mc_g + i)
+                         : "memory");
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const uint64_t i = base + (uint64_t)u * 2048;
+        if (!ok[u]) continue;
+        const uint4 q = Q[u];
         f8 P = ld8(p + i), M = ld8(m + i), V = ld8(v + i);
         float G[8];
         G[0] = bf16_bits_to_f32(q.x & 0xffffu); G[1] = bf16_bits_to_f32(q.x >> 16);
