@@ -115,6 +115,7 @@ def run_finetune(model_name: str, batch: int, seq: int, steps: int, warmup: int,
             "loss_last": losses[-1], "build_seconds": build_s,
             "max_memory_gb": torch.cuda.max_memory_allocated(dev) / 2**30,
             "e2e": {"h2d_bytes_per_step": batch * seq * 8 * world, "d2h_bytes_per_step": 4 * world}}
+    engine.close()
     del engine, model
     import gc
     gc.collect()

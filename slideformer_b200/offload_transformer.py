@@ -234,10 +234,33 @@ class SlideFormerOffloader(nn.Module):
                 module.wait_for_h2d()
             return None
 
+        self._hook_handles = []
         for unit in units:
-            unit.register_forward_pre_hook(pre_forward)
-            unit.register_forward_hook(post_forward)
-            unit.register_full_backward_pre_hook(pre_backward)
+            self._hook_handles += [unit.register_forward_pre_hook(pre_forward), unit.register_forward_hook(post_forward),
+                                   unit.register_full_backward_pre_hook(pre_backward)]
+
+    def close(self):
+        """Drain the last step and release everything the engine holds on the GPU and in pinned host
+        memory: hooks, units, optimizer state, gradient and window rings, the activation store.
+        Autograd keeps hook callables where Python's cycle collector cannot see them, so an engine
+        that is merely dropped stays alive; call this before building another one."""
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
+        self.wait_for_completion()
+        for h in self._hook_handles:
+            h.remove()
+        self._hook_handles = []
+        for unit in self.transformer_layers:
+            unit.close()
+        opt = self.layer_optimizer
+        opt.exp_avg_flat.clear()
+        opt.exp_avg_sq_flat.clear()
+        opt.state.clear()
+        opt.param_groups.clear()
+        opt._scratch = {}
+        self._grad_pool = self.weight_pool = self.activation_store = None
+        self._deferred = []
 
     def wait_for_completion(self) -> None:
         """Drain the step: flush units whose backward left parameters untouched, make the compute

@@ -271,9 +271,12 @@ class OffloadLayerWrapper(nn.Module):
             for bname, buf in module.named_buffers(recurse=False):
                 if buf is not None and not buf.is_meta and buf.device != device:
                     module._buffers[bname] = buf.to(device)
+        # autograd keeps these callables on the C++ side, where Python's cycle collector cannot see
+        # them: close() removes them, otherwise the unit (and its HBM) outlives its last reference
+        self._hook_handles = []
         for _, p in self._managed_named_params:
             if p.requires_grad:
-                p.register_post_accumulate_grad_hook(self._on_param_grad)
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._on_param_grad))
 
     # ---- window management (names of transformer_layer.py:273-343) ------------------------------
     def to_device_async(self, is_bwd: bool = False, bwd_phase: Optional[bool] = None):
@@ -434,6 +437,22 @@ class OffloadLayerWrapper(nn.Module):
             p.grad = None
         self.host_update_seconds += time.perf_counter() - _h0
         return self.update_done
+
+    def close(self):
+        """Release the unit: remove the gradient hooks and drop every large buffer it owns.  The
+        module is unusable afterwards."""
+        for h in self._hook_handles:
+            h.remove()
+        self._hook_handles = []
+        for _, p in self._managed_named_params:
+            p.grad = None
+            p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+        self._params_flat = self._bf16_flat = self._bf16_host = None
+        self._master_views, self._bf16_views = [], []
+        self._unit = self._wunit = self.own_grad_unit = None
+        self.grad_pool = self.weight_pool = self.defer_to = None
+        self._dp_state = None
+        self.timings = {}
 
     def wait_for_update(self):
         """Order the compute stream after this unit's last optimizer step."""
