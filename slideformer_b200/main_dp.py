@@ -48,6 +48,12 @@ def parse_args(argv=None) -> argparse.Namespace:
     ap.add_argument("--batch-size", type=int, default=1, help="sequences per rank and step")
     ap.add_argument("--seq-length", type=int, default=32, help="length of the synthetic sequences of --tiny")
     ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--warmup-steps", type=int, default=0,
+                    help="with --total-steps: linear warm-up then cosine decay of the learning rate")
+    ap.add_argument("--total-steps", type=int, default=0, help="length of the cosine schedule (0 = constant lr)")
+    ap.add_argument("--clip-norm", type=float, default=0.0,
+                    help="clip the global gradient norm to this value, using the norm measured by the previous step's "
+                         "update kernels (0 = off)")
     ap.add_argument("--chunk-numel", type=int, default=1 << 25, help="elements per optimizer call")
     ap.add_argument("--double-buffer", action="store_true", help="three gradient units instead of two")
     ap.add_argument("--tied", action="store_true", help="--tiny with tied input/output embeddings")
@@ -173,8 +179,17 @@ def main(argv=None) -> int:
     before = [w.clone() for w in owned_master_weights(engine)] if ns.tiny else []
     torch.manual_seed(1234 + ranks.rank)   # anything stochastic from here on differs per rank
 
+    sched = None
+    if ns.total_steps > 0:
+        from slideformer_b200.lr_schedule import WarmupCosine
+        sched = WarmupCosine(engine, ns.lr, ns.warmup_steps, ns.total_steps)
+    if ns.clip_norm > 0:
+        engine.enable_grad_stats()
+
     done = 0
     for done in range(1, ns.steps + 1):
+        if sched is not None:
+            sched.step()
         ids = next(stream).to(ranks.device)
         loss = engine(ids, labels=ids).loss
         if not all_ranks_finite(loss, ranks):
@@ -182,8 +197,15 @@ def main(argv=None) -> int:
         loss.backward()
         engine.wait_for_completion()
         shown = mean_over_ranks(loss, ranks)
+        extra = ""
+        if ns.clip_norm > 0:
+            stats = engine.read_grad_stats()
+            if stats["nonfinite"]:
+                raise RuntimeError("Nonfinite gradient on at least one rank")
+            scale = engine.clip_scale_for_next_step(ns.clip_norm, stats)
+            extra = f" grad_norm={stats['norm']:.6f} next_clip={scale:.4f}"
         if ranks.rank == 0:
-            print(f"step={done} global_loss={shown:.6f} ranks={ranks.world}", flush=True)
+            print(f"step={done} global_loss={shown:.6f} ranks={ranks.world}{extra}", flush=True)
 
     if ns.tiny:
         self_check(engine, before, done, dp)

@@ -343,6 +343,39 @@ class SlideFormerOffloader(nn.Module):
     def update_learning_rate(self, new_lr):
         self.layer_optimizer.update_learning_rate(new_lr)
 
+    # ---- gradient-side work folded into the update kernels ------------------------------------------
+    def enable_grad_stats(self):
+        """Every update of the coming steps also accumulates sum(g*g) and a non-finite flag of the
+        gradients it consumes (no extra pass over HBM); read them with `read_grad_stats`."""
+        self.layer_optimizer.enable_grad_stats(self.device)
+
+    def set_grad_scale(self, scale: float):
+        """Multiply every gradient by `scale` inside the update kernels of the coming steps."""
+        self.layer_optimizer.set_grad_scale(scale)
+
+    def read_grad_stats(self, reset: bool = True) -> dict:
+        """Global gradient statistics of the step(s) since the last reset: {"sumsq", "norm",
+        "nonfinite"}.  Under `shared_dp` every rank measured the slices it owns of the MEAN
+        gradient; the parts are summed over the ranks here (a collective: call it on every rank)."""
+        self.wait_for_completion()
+        st = self.layer_optimizer.read_grad_stats(reset)
+        if self.shared_dp is not None:
+            import torch.distributed as dist
+            t = torch.tensor([st["sumsq"], 1.0 if st["nonfinite"] else 0.0], dtype=torch.float64, device=self.device)
+            dist.all_reduce(t)
+            st = {"sumsq": float(t[0]), "norm": float(t[0]) ** 0.5, "nonfinite": bool(t[1] > 0)}
+        return st
+
+    def clip_scale_for_next_step(self, max_norm: float, stats: Optional[dict] = None) -> float:
+        """Delayed global-norm clipping: derive the multiplier for the NEXT step from the norm the
+        last step measured (a layer-wise optimizer has already applied the first layers' updates
+        when the last layer's gradient, and with it the step's own norm, exists)."""
+        stats = stats if stats is not None else self.read_grad_stats()
+        norm = stats["norm"]      # taken before the multiplier is applied: the raw gradient's norm
+        new = 1.0 if (stats["nonfinite"] or norm <= max_norm or norm == 0.0) else max_norm / norm
+        self.set_grad_scale(new)
+        return new
+
     def parameter_update_ms(self):
         """Per-unit mean device time of the optimizer step (needs enable_timing)."""
         out = {}

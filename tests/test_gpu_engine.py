@@ -261,6 +261,28 @@ def test_timer_labels_and_stats(capsys):
         assert label in text, label
 
 
+def test_engine_grad_stats_match_the_gradients_it_consumed():
+    """sum(g*g) gathered inside the update kernels equals the norm of the flat gradients the engine
+    handed to the optimizer, and a multiplier of 1/2 halves the first step's Adam moments."""
+    eng, _ = _make("llama-tiny")
+    eng.enable_grad_stats()
+    grabbed = _capture_grads(eng)
+    ids = _ids(eng.config.vocab_size, 2, 32, 1, seed=21)[0]
+    eng(ids, labels=ids).loss.backward()
+    st = eng.read_grad_stats()
+    want = sum(float(g.float().double().pow(2).sum()) for g in grabbed.values())
+    assert st["nonfinite"] is False and st["sumsq"] == pytest.approx(want, rel=1e-4)
+    assert eng.clip_scale_for_next_step(st["norm"] * 0.5, st) == pytest.approx(0.5)
+    assert eng.clip_scale_for_next_step(st["norm"] * 2.0, st) == 1.0
+    half, _ = _make("llama-tiny")
+    half.set_grad_scale(0.5)
+    half(ids, labels=ids).loss.backward()
+    half.wait_for_completion()
+    m_full = eng.layer_optimizer.exp_avg_flat[1]
+    m_half = half.layer_optimizer.exp_avg_flat[1]
+    assert torch.allclose(m_half * 2, m_full, rtol=1e-6, atol=1e-30)   # m = (1 - beta1) * g after one step; halving g is exact
+
+
 def test_close_releases_the_engine_memory():
     """Autograd holds the gradient hooks where the cycle collector cannot see them; close() is what
     returns an engine's HBM (a benchmark that builds several engines in one process needs it)."""

@@ -26,7 +26,19 @@ def test_tiny_single_gpu(tmp_path):
     assert (tmp_path / "m" / "config.json").exists()
 
 
-@pytest.mark.parametrize("extra", [[], ["--tied"], ["--double-buffer", "--chunk-numel", "4096"]])
+def test_tiny_single_gpu_with_schedule_and_clipping():
+    """Warm-up + cosine schedule and delayed global-norm clipping driven by the statistics the
+    update kernels gather."""
+    out = _run([sys.executable, "-m", "slideformer_b200.main_dp", "--tiny", "--steps", "4", "--batch-size", "2",
+                "--warmup-steps", "2", "--total-steps", "10", "--clip-norm", "0.05"])
+    assert "rank=0 completed=4" in out
+    norms = [float(line.split("grad_norm=")[1].split()[0]) for line in out.splitlines() if "grad_norm=" in line]
+    clips = [float(line.split("next_clip=")[1].split()[0]) for line in out.splitlines() if "next_clip=" in line]
+    assert len(norms) == 4 and all(n > 0 for n in norms)
+    assert all(abs(c - min(1.0, 0.05 / n)) < 1e-3 for n, c in zip(norms, clips))
+
+
+@pytest.mark.parametrize("extra", [[], ["--tied"], ["--double-buffer", "--chunk-numel", "4096"], ["--clip-norm", "0.05"]])
 def test_tiny_two_gpus(extra):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
