@@ -304,13 +304,13 @@ def test_close_releases_the_engine_memory():
         ids = _ids(eng.config.vocab_size, 2, 32, 1)[0]
         eng(ids, labels=ids).loss.backward()
         eng.wait_for_completion()
-        assert torch.cuda.memory_allocated() - before > (1 << 20)
+        assert torch.cuda.memory_allocated() - before > (256 << 10)
         eng.close()
         eng.close()                      # idempotent
         del eng, ids
         gc.collect()
         torch.cuda.empty_cache()
-        assert torch.cuda.memory_allocated() - before < (1 << 20), kw
+        assert torch.cuda.memory_allocated() - before < (64 << 10), kw
 
 
 def test_inference_forward_and_lr_update():
