@@ -254,9 +254,11 @@ int sf_adam_update_dp_static(int id, uint64_t step, float lr, float beta1, float
  * chunk_elems must be a multiple of 16 (so every chunk but the last stays on the vector
  * body, like the reference's 32 Mi-element chunks, transformer_layer.py:26-27).  The scalar
  * state machine advances once (one reference call per chunk would take the pow() branch
- * from the second chunk on; pass per_chunk_scalars != 0 to reproduce that).  All calls that
+ * from the second chunk on; pass per_chunk_scalars != 0 to reproduce that).  Inside a chunk the
+ * data moves in smaller pieces (sf_set_host_piece) through the scratch slots.  All calls that
  * target one device share one set of internal streams and events: issue them from one thread
- * at a time. */
+ * at a time.  Two calls issued back to back from DIFFERENT streams overlap: the second one's
+ * uploads start while the first one's downloads drain. */
 size_t sf_adam_host_scratch_bytes(uint64_t chunk_elems, int g_dtype, int g_on_host);
 int sf_adam_update_host(int id, uint64_t step, float lr, float beta1, float beta2, float eps,
                         float weight_decay, int bias_correction, float* p_host,
@@ -289,6 +291,11 @@ int sf_set_tuning(int variant, int ctas_per_sm);
  * thread is issued before the first add; 0 = always the runtime-world kernel.  Negative values
  * keep the current setting; the defaults are (8, 1).  For benchmarking; not thread safe. */
 int sf_set_push_tuning(int vec, int specialise_world);
+
+/* Elements per piece of the host-streaming pipeline (sf_adam_update_host): a chunk is cut into
+ * pieces of at most this many elements that move through up to eight scratch slots.  A multiple
+ * of 16; default 8 Mi.  Results do not depend on it.  Not thread safe. */
+int sf_set_host_piece(uint64_t piece_elems);
 
 /* 8-element groups per thread of the NVLS kernel (sf_adam_step_sharded_nvls): 1, 2 or 4
  * in-switch reductions in flight per thread.  For benchmarking; not thread safe. */

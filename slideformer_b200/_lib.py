@@ -82,6 +82,7 @@ SIGNATURES = {
     "sf_set_tuning": (_i, [_i, _i]),
     "sf_set_push_tuning": (_i, [_i, _i]),
     "sf_set_nvls_tuning": (_i, [_i]),
+    "sf_set_host_piece": (_i, [_u64]),
     "sf_copy_bytes": (_i, [_vp, _vp, C.c_size_t, _vp]),
     "sf_dev_alloc": (_i, [C.c_size_t, C.POINTER(_vp)]),
     "sf_dev_free": (_i, [_vp]),

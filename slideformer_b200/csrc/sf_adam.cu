@@ -258,10 +258,15 @@ int step_impl(const SfAdamScalars* s, float* p, const void* g, int g_dtype, floa
 }
 
 // ---- host-streaming resources: three side streams and per-slot events, one set per device ---
+constexpr int kHostSlots = 8;
 struct HostPipe {
     cudaStream_t s_in = nullptr, s_k = nullptr, s_out = nullptr;
-    cudaEvent_t ev_start = nullptr, ev_in[2] = {nullptr, nullptr}, ev_k[2] = {nullptr, nullptr},
-                ev_out[2] = {nullptr, nullptr}, ev_done = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_in[kHostSlots] = {}, ev_k[kHostSlots] = {}, ev_out[kHostSlots] = {},
+                ev_done = nullptr;
+    uint64_t next_slot = 0;   // slots are handed out round-robin across calls
+    const void* last_base = nullptr;   // scratch layout of the previous call: slot events only
+    size_t last_slot_bytes = 0;        // guard a slot's memory while the layout stays the same
+    int last_nslots = 0;
     bool ready = false;
 };
 std::mutex g_pipe_mu;
@@ -279,7 +284,7 @@ int get_pipe(HostPipe** out)
         SF_CUDA(cudaStreamCreateWithFlags(&hp.s_out, cudaStreamNonBlocking));
         SF_CUDA(cudaEventCreateWithFlags(&hp.ev_start, cudaEventDisableTiming));
         SF_CUDA(cudaEventCreateWithFlags(&hp.ev_done, cudaEventDisableTiming));
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < kHostSlots; i++) {
             SF_CUDA(cudaEventCreateWithFlags(&hp.ev_in[i], cudaEventDisableTiming));
             SF_CUDA(cudaEventCreateWithFlags(&hp.ev_k[i], cudaEventDisableTiming));
             SF_CUDA(cudaEventCreateWithFlags(&hp.ev_out[i], cudaEventDisableTiming));
@@ -606,49 +611,71 @@ int sf_adam_update_host(int id, uint64_t step, float lr, float beta1, float beta
     if (int rc = get_pipe(&hp)) return rc;
     cudaStream_t user = (cudaStream_t)stream;
     const size_t gsz = g_dtype == SF_GRAD_BF16 ? 2 : 4;
-    const size_t arr = round256((size_t)chunk_elems * 4);
-    const size_t garr = g_on_host ? round256((size_t)chunk_elems * gsz) : 0;
+    // A chunk is one reference call; inside it the copies and launches move in PIECES of at most
+    // g_tune.host_piece elements through up to eight scratch slots, so that a call's first upload
+    // and last download (the only copies nothing of the same call overlaps) stay short and the
+    // tail of one call overlaps the head of the next one issued from another stream.
+    uint64_t piece = g_tune.host_piece < chunk_elems ? g_tune.host_piece : chunk_elems;
+    piece = piece < 16 ? 16 : (piece & ~(uint64_t)15);
+    const size_t arr = round256((size_t)piece * 4);
+    const size_t garr = g_on_host ? round256((size_t)piece * gsz) : 0;
     const size_t slot_bytes = 3 * arr + garr;
+    int nslots = (int)(scratch_bytes / slot_bytes);
+    nslots = nslots > kHostSlots ? kHostSlots : nslots;
+    if (nslots < 2) return fail(SF_ERR_SIZE, "scratch is too small for two pipeline slots");
     char* base = (char*)scratch;
 
     SF_CUDA(cudaEventRecord(hp->ev_start, user));
     SF_CUDA(cudaStreamWaitEvent(hp->s_in, hp->ev_start, 0));
     SF_CUDA(cudaStreamWaitEvent(hp->s_k, hp->ev_start, 0));
     SF_CUDA(cudaStreamWaitEvent(hp->s_out, hp->ev_start, 0));
+    if (hp->last_base != scratch || hp->last_slot_bytes != slot_bytes || hp->last_nslots != nslots) {
+        // another scratch buffer or slot layout than last time: let every copy of the earlier
+        // calls finish before this call's slots are written
+        SF_CUDA(cudaStreamWaitEvent(hp->s_in, hp->ev_done, 0));
+        hp->last_base = scratch;
+        hp->last_slot_bytes = slot_bytes;
+        hp->last_nslots = nslots;
+    }
 
     const uint64_t nchunks = (n + chunk_elems - 1) / chunk_elems;
     for (uint64_t k = 0; k < nchunks; k++) {
-        const int slot = (int)(k & 1);
-        const uint64_t lo = k * chunk_elems;
-        const uint64_t len = (lo + chunk_elems <= n) ? chunk_elems : n - lo;
-        float* dp = (float*)(base + slot * slot_bytes);
-        float* dm = (float*)(base + slot * slot_bytes + arr);
-        float* dv = (float*)(base + slot * slot_bytes + 2 * arr);
-        void* dg = g_on_host ? (void*)(base + slot * slot_bytes + 3 * arr) : (void*)((const char*)g + lo * gsz);
-        // the slot is free once the device->host copies of its previous user are done (chunk
-        // k-2 of this call, or a chunk of an earlier call; waiting on a never-recorded event
-        // is a no-op)
-        SF_CUDA(cudaStreamWaitEvent(hp->s_in, hp->ev_out[slot], 0));
-        SF_CUDA(cudaMemcpyAsync(dp, p_host + lo, len * 4, cudaMemcpyHostToDevice, hp->s_in));
-        SF_CUDA(cudaMemcpyAsync(dm, m_host + lo, len * 4, cudaMemcpyHostToDevice, hp->s_in));
-        SF_CUDA(cudaMemcpyAsync(dv, v_host + lo, len * 4, cudaMemcpyHostToDevice, hp->s_in));
-        if (g_on_host)
-            SF_CUDA(cudaMemcpyAsync(dg, (const char*)g + lo * gsz, len * gsz, cudaMemcpyHostToDevice, hp->s_in));
-        SF_CUDA(cudaEventRecord(hp->ev_in[slot], hp->s_in));
-
-        SF_CUDA(cudaStreamWaitEvent(hp->s_k, hp->ev_in[slot], 0));
+        const uint64_t c_lo = k * chunk_elems;
+        const uint64_t c_hi = (c_lo + chunk_elems <= n) ? c_lo + chunk_elems : n;
         if (k > 0 && per_chunk_scalars)
             if (int rc = sf_adam_scalars(id, step, lr, beta1, beta2, eps, weight_decay, bias_correction, &s)) return rc;
-        if (int rc = step_impl(&s, dp, dg, g_dtype, dm, dv, p_bf16_dev ? p_bf16_dev + lo : nullptr, len,
-                               len & ~(uint64_t)15, hp->s_k))
-            return rc;
-        SF_CUDA(cudaEventRecord(hp->ev_k[slot], hp->s_k));
+        for (uint64_t lo = c_lo; lo < c_hi; lo += piece) {
+            const uint64_t len = (lo + piece <= c_hi) ? piece : c_hi - lo;
+            const int slot = (int)(hp->next_slot++ % (uint64_t)nslots);
+            float* dp = (float*)(base + slot * slot_bytes);
+            float* dm = (float*)(base + slot * slot_bytes + arr);
+            float* dv = (float*)(base + slot * slot_bytes + 2 * arr);
+            void* dg = g_on_host ? (void*)(base + slot * slot_bytes + 3 * arr) : (void*)((const char*)g + lo * gsz);
+            // the slot is free once the device->host copies of its previous user are done (an
+            // earlier piece of this call or of an earlier call; waiting on a never-recorded event
+            // is a no-op)
+            SF_CUDA(cudaStreamWaitEvent(hp->s_in, hp->ev_out[slot], 0));
+            SF_CUDA(cudaMemcpyAsync(dp, p_host + lo, len * 4, cudaMemcpyHostToDevice, hp->s_in));
+            SF_CUDA(cudaMemcpyAsync(dm, m_host + lo, len * 4, cudaMemcpyHostToDevice, hp->s_in));
+            SF_CUDA(cudaMemcpyAsync(dv, v_host + lo, len * 4, cudaMemcpyHostToDevice, hp->s_in));
+            if (g_on_host)
+                SF_CUDA(cudaMemcpyAsync(dg, (const char*)g + lo * gsz, len * gsz, cudaMemcpyHostToDevice, hp->s_in));
+            SF_CUDA(cudaEventRecord(hp->ev_in[slot], hp->s_in));
 
-        SF_CUDA(cudaStreamWaitEvent(hp->s_out, hp->ev_k[slot], 0));
-        SF_CUDA(cudaMemcpyAsync(p_host + lo, dp, len * 4, cudaMemcpyDeviceToHost, hp->s_out));
-        SF_CUDA(cudaMemcpyAsync(m_host + lo, dm, len * 4, cudaMemcpyDeviceToHost, hp->s_out));
-        SF_CUDA(cudaMemcpyAsync(v_host + lo, dv, len * 4, cudaMemcpyDeviceToHost, hp->s_out));
-        SF_CUDA(cudaEventRecord(hp->ev_out[slot], hp->s_out));
+            SF_CUDA(cudaStreamWaitEvent(hp->s_k, hp->ev_in[slot], 0));
+            // piece boundaries are multiples of 16, so only the last piece of a chunk can hold the
+            // chunk's scalar tail: the same split as one launch over the whole chunk
+            if (int rc = step_impl(&s, dp, dg, g_dtype, dm, dv, p_bf16_dev ? p_bf16_dev + lo : nullptr, len,
+                                   len & ~(uint64_t)15, hp->s_k))
+                return rc;
+            SF_CUDA(cudaEventRecord(hp->ev_k[slot], hp->s_k));
+
+            SF_CUDA(cudaStreamWaitEvent(hp->s_out, hp->ev_k[slot], 0));
+            SF_CUDA(cudaMemcpyAsync(p_host + lo, dp, len * 4, cudaMemcpyDeviceToHost, hp->s_out));
+            SF_CUDA(cudaMemcpyAsync(m_host + lo, dm, len * 4, cudaMemcpyDeviceToHost, hp->s_out));
+            SF_CUDA(cudaMemcpyAsync(v_host + lo, dv, len * 4, cudaMemcpyDeviceToHost, hp->s_out));
+            SF_CUDA(cudaEventRecord(hp->ev_out[slot], hp->s_out));
+        }
     }
     // s_out is ordered after the last kernel; make the caller's stream wait for everything.
     SF_CUDA(cudaEventRecord(hp->ev_done, hp->s_out));
@@ -667,6 +694,13 @@ int sf_copy_bytes(void* dst, const void* src, size_t bytes, void* stream)
     if (!aligned(dst, 16) || !aligned(src, 16) || (bytes & 15))
         return fail(SF_ERR_ALIGN, "dst, src and bytes must be multiples of 16");
     return launch_copy16(dst, src, bytes / 16, (cudaStream_t)stream);
+}
+
+int sf_set_host_piece(uint64_t piece_elems)
+{
+    if (piece_elems < 16 || (piece_elems & 15)) return fail(SF_ERR_ARG, "piece_elems must be a positive multiple of 16");
+    g_tune.host_piece = piece_elems;
+    return SF_OK;
 }
 
 int sf_set_nvls_tuning(int groups_per_thread)

@@ -27,6 +27,7 @@ struct Tuning {
                           // grid of SMs * k CTAs walking the tiles
     int push_vec = 8;     // elements per thread of the fused pull+push kernel: 4 or 8
     int push_world = 1;   // 1: kernels specialised for world 2 / 4 / 8; 0: runtime world only
+    uint64_t host_piece = 8u << 20;  // elements per copy / launch piece of the host-streaming pipeline
     int nvls_groups = 1;  // 8-element groups per thread of the NVLS kernel: 1, 2 or 4 (measured equal: 0.90 ms at 8 GPUs)
 };
 extern Tuning g_tune;

@@ -120,6 +120,7 @@ class SlideFormerOffloader(nn.Module):
 
         with torch.cuda.device(device):
             self.opt_stream = torch.cuda.Stream()
+            self.opt_stream_alt = torch.cuda.Stream()
         n_units = min(3 if double_buffer else 2, len(self.decoder_layers) + 2)
         self.gpu_unit_size = n_units
         # Small models under data parallelism: every unit keeps its own exchange slot and all units
@@ -171,7 +172,8 @@ class SlideFormerOffloader(nn.Module):
             self.state_placement = plan_state_placement(sizes, budget)
             self.hbm_state_budget_bytes = budget
         kwargs = dict(weight_pool=self.weight_pool, comm_stream=self.comm_stream,
-                      opt_stream=self.opt_stream, enable_timing=enable_timing, layer_optimizer=self.layer_optimizer,
+                      opt_stream=self.opt_stream, opt_stream_alt=self.opt_stream_alt, enable_timing=enable_timing,
+                      layer_optimizer=self.layer_optimizer,
                       state_device=("hbm" if state_device == "auto" else state_device), shared_dp=shared_dp,
                       activation_checkpoint=activation_checkpoint, loss_chunk_tokens=loss_chunk_tokens,
                       enable_nvtx=enable_nvtx)
@@ -269,6 +271,7 @@ class SlideFormerOffloader(nn.Module):
             unit.flush()
         self._update_deferred_units()
         torch.cuda.current_stream(self.device).wait_stream(self.opt_stream)
+        torch.cuda.current_stream(self.device).wait_stream(self.opt_stream_alt)
         torch.cuda.synchronize(self.device)
 
     def _update_deferred_units(self):

@@ -148,7 +148,8 @@ class OffloadLayerWrapper(nn.Module):
                  tied_param: Optional[nn.Parameter] = None, enable_timing: bool = False, is_last_layer: bool = False,
                  layer_optimizer=None, dtype: torch.dtype = torch.bfloat16, state_device: str = "hbm",
                  shared_dp=None, update_chunk: int = UPDATE_CHUNK_SIZE, weight_pool: Optional[WeightUnitPool] = None,
-                 comm_stream: Optional[torch.cuda.Stream] = None, init_seed: int = 0, enable_nvtx: bool = True):
+                 comm_stream: Optional[torch.cuda.Stream] = None, init_seed: int = 0, enable_nvtx: bool = True,
+                 opt_stream_alt: Optional[torch.cuda.Stream] = None):
         super().__init__()
         if layer_optimizer is None:
             raise RuntimeError("a shared LayerAdam must be provided")
@@ -158,6 +159,13 @@ class OffloadLayerWrapper(nn.Module):
         self.layer = layer
         self.grad_pool = grad_pool
         self.opt_stream = opt_stream
+        # Units whose state streams from host memory alternate between two optimizer streams: the
+        # library's copies of two calls issued from different streams overlap (the uploads of one
+        # unit start while the downloads of the previous one drain)
+        # (not with the one-GPU weight window, whose single bf16 staging buffer relies on one stream)
+        if (state_device == "host" and shared_dp is None and opt_stream_alt is not None and weight_pool is None
+                and (layer_idx & 1)):
+            self.opt_stream = opt_stream_alt
         self.layer_optimizer = layer_optimizer
         self.state_device = state_device
         self.shared_dp = shared_dp
