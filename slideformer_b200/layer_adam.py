@@ -178,12 +178,16 @@ class LayerAdam:
                 raise RuntimeError("params, grads and moments must be on the same CUDA device")
             if bf16 is not None and bf16.device != p.device:
                 raise RuntimeError("bf16 output must be on the parameter's device")
-            with torch.cuda.device(p.device):
-                stream = torch.cuda.current_stream().cuda_stream
-                _lib.check(self._lib.sf_adam_update(
-                    self.optimizer_id, int(step), lr, beta1, beta2, eps, weight_decay, int(bias_correction == 1),
+            args = (self.optimizer_id, int(step), lr, beta1, beta2, eps, weight_decay, int(bias_correction == 1),
                     p.data_ptr(), g.data_ptr(), gcode, m.data_ptr(), v.data_ptr(),
-                    bf16.data_ptr() if bf16 is not None else None, n, stream))
+                    bf16.data_ptr() if bf16 is not None else None, n)
+            if p.device.index == torch.cuda.current_device():   # the usual case: no device switch to pay for
+                rc = self._lib.sf_adam_update(*args, torch.cuda.current_stream().cuda_stream)
+            else:
+                with torch.cuda.device(p.device):
+                    rc = self._lib.sf_adam_update(*args, torch.cuda.current_stream().cuda_stream)
+            if rc:
+                _lib.check(rc)
             return
         if p.device.type != "cpu":
             raise RuntimeError(f"unsupported device type: {p.device.type}")
