@@ -43,8 +43,11 @@ typedef enum SfStatus {
 } SfStatus;
 
 /* Gradient element type.  Parameters, exp_avg and exp_avg_sq are always fp32: the triples
- * <float, BFloat16, float> and <float, float, float> of cpu_adam_impl.cpp:187-188. */
-typedef enum SfGradDtype { SF_GRAD_BF16 = 0, SF_GRAD_F32 = 1 } SfGradDtype;
+ * <float, BFloat16, float>, <float, float, float> and <float, Half, float> of
+ * cpu_adam_impl.cpp:187-189, which are the ones a caller with fp32 master weights can reach
+ * (the reference's other six have 16-bit parameters).  fp16 gradients are accepted by the
+ * single-GPU and host-streaming entry points; the data-parallel exchange takes bf16 or fp32. */
+typedef enum SfGradDtype { SF_GRAD_BF16 = 0, SF_GRAD_F32 = 1, SF_GRAD_F16 = 2 } SfGradDtype;
 
 /* Gradient statistics gathered by the same pass that applies the update, so that a loss-health
  * check (the reference tests isfinite(loss), multi_gpu/scripts/main_dp.py:102-105) or a
@@ -115,7 +118,7 @@ int sf_adam_set_grad_hooks(int id, float grad_scale, SfGradStats* grad_stats_dev
 /* Replaces ds_adam_step / adam_update (cpu_adam_impl.cpp:220-270) for device buffers:
  * sf_adam_scalars(id, ...) followed by sf_adam_step(...) with vec_n = n rounded down to 16.
  *   p, m, v   fp32[n], updated in place
- *   g         bf16[n] or fp32[n] according to g_dtype, read only
+ *   g         bf16[n], fp32[n] or fp16[n] according to g_dtype, read only
  *   p_bf16    optional bf16[n] output: round-to-nearest-even copy of the UPDATED p, NaN ->
  *             0x7FC0.  Replaces the reference's separate CPU cast, transformer_layer.py:296-305.
  * Any n >= 0 and any natural element alignment is accepted.  The 128-bit vector kernel runs

@@ -120,6 +120,35 @@ static inline float bf16_to_f32(uint16_t h)
     return f;
 }
 
+/* IEEE binary16 -> binary32, exact (the reference widens with _mm512_cvtph_ps, simd.h; its
+ * scalar tail converts through c10::Half).  Subnormals, infinities and NaN payloads included. */
+static inline float f16_to_f32(uint16_t h)
+{
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    uint32_t u;
+    if (exp == 0) {
+        if (man == 0) {
+            u = sign;
+        } else {
+            int e = -1;
+            do {
+                man <<= 1;
+                e++;
+            } while (!(man & 0x400u));
+            u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) {
+        u = sign | 0x7f800000u | (man << 13);
+    } else {
+        u = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
 /* simd.h:56-86 and c10::BFloat16 round_to_nearest_even: RNE on the upper 16 bits,
  * every NaN becomes 0x7FC0. */
 static inline uint16_t f32_to_bf16_rne(float f)
@@ -205,6 +234,22 @@ void oracle_step_f32_f32(const oracle_consts_t* c, float* p, const float* g, flo
     }
     for (size_t i = vec_n; i < n; i++) {
         tail_elem(c, p + i, g[i], m + i, v + i);
+        if (p_bf16) p_bf16[i] = f32_to_bf16_rne(p[i]);
+    }
+}
+
+/* <float, Half, float>, cpu_adam_impl.cpp:189. */
+void oracle_step_f32_f16(const oracle_consts_t* c, float* p, const uint16_t* g, float* m,
+                         float* v, uint16_t* p_bf16, size_t n, size_t vec_n)
+{
+    if (vec_n > n) vec_n = n;
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < vec_n; i++) {
+        body_elem(c, p + i, f16_to_f32(g[i]), m + i, v + i);
+        if (p_bf16) p_bf16[i] = f32_to_bf16_rne(p[i]);
+    }
+    for (size_t i = vec_n; i < n; i++) {
+        tail_elem(c, p + i, f16_to_f32(g[i]), m + i, v + i);
         if (p_bf16) p_bf16[i] = f32_to_bf16_rne(p[i]);
     }
 }

@@ -58,7 +58,7 @@ def lib():
         L.oracle_increment_step.argtypes = [C.POINTER(_Adam), C.c_uint64, C.c_float, C.c_float]
         L.oracle_update_state.argtypes = [C.POINTER(_Adam), C.c_float, C.c_float, C.c_float, C.c_int]
         L.oracle_consts.argtypes = [C.POINTER(_Adam), C.POINTER(Consts)]
-        for name in ("oracle_step_f32_bf16", "oracle_step_f32_f32"):
+        for name in ("oracle_step_f32_bf16", "oracle_step_f32_f32", "oracle_step_f32_f16"):
             getattr(L, name).argtypes = [C.POINTER(Consts), C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]
             getattr(L, name).restype = None
@@ -110,6 +110,8 @@ def apply_step(c: Consts, p, g, m, v, p_bf16=None, vec_n=None):
         fn = lib().oracle_step_f32_bf16
     elif g.dtype == np.float32:
         fn = lib().oracle_step_f32_f32
+    elif g.dtype == np.float16:
+        fn = lib().oracle_step_f32_f16
     else:
         raise TypeError(f"unsupported gradient dtype {g.dtype}")
     if p_bf16 is not None:

@@ -13,7 +13,7 @@ LIB_PATH = PKG / "libslideformer_b200.so"
 
 SF_OK = 0
 SF_ERR_NULL, SF_ERR_ALIGN, SF_ERR_SIZE, SF_ERR_UNKNOWN_ID, SF_ERR_CUDA, SF_ERR_DTYPE, SF_ERR_ARG = range(1, 8)
-SF_GRAD_BF16, SF_GRAD_F32 = 0, 1
+SF_GRAD_BF16, SF_GRAD_F32, SF_GRAD_F16 = 0, 1, 2
 SF_IPC_HANDLE_BYTES = 64
 SF_ABI_VERSION = 2
 SF_STATIC_SCRATCH_MAX_ELEMS = 4 << 20  # sf_adam_update_dp_static: largest n per call

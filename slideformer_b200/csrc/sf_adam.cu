@@ -223,16 +223,23 @@ int launch_vec8(const StepCtx& x, float* p, const void* g, float* m, float* v, u
     });
 }
 
+// Gradient dtypes of the single-GPU and host-streaming entry points.
+inline bool local_dtype_ok(int g_dtype) { return g_dtype == SF_GRAD_BF16 || g_dtype == SF_GRAD_F32 || g_dtype == SF_GRAD_F16; }
+inline size_t grad_elem_size(int g_dtype) { return g_dtype == SF_GRAD_F32 ? 4 : 2; }
+int bad_local_dtype(int g_dtype)
+{
+    return fail(SF_ERR_DTYPE, "gradient dtype code " + std::to_string(g_dtype) + " is not supported (0 = bf16, 1 = fp32, 2 = fp16)");
+}
+
 int step_impl(const SfAdamScalars* s, float* p, const void* g, int g_dtype, float* m, float* v,
               uint16_t* out, uint64_t n, uint64_t vec_n, cudaStream_t st)
 {
     if (!s) return fail(SF_ERR_NULL, "scalars pointer is NULL");
-    if (g_dtype != SF_GRAD_BF16 && g_dtype != SF_GRAD_F32)
-        return fail(SF_ERR_DTYPE, "gradient dtype code " + std::to_string(g_dtype) + " is not supported (0 = bf16, 1 = fp32)");
+    if (!local_dtype_ok(g_dtype)) return bad_local_dtype(g_dtype);
     if (n == 0) return SF_OK;
     if (!p || !g || !m || !v) return fail(SF_ERR_NULL, "p, g, m and v must be non-NULL when n > 0");
     if (n > ((uint64_t)1 << 40)) return fail(SF_ERR_SIZE, "n exceeds 2^40 elements");
-    if (!aligned(p, 4) || !aligned(m, 4) || !aligned(v, 4) || !aligned(g, g_dtype == SF_GRAD_BF16 ? 2 : 4) ||
+    if (!aligned(p, 4) || !aligned(m, 4) || !aligned(v, 4) || !aligned(g, grad_elem_size(g_dtype)) ||
         !aligned(out, 2))
         return fail(SF_ERR_ALIGN, "a buffer is not aligned to its element size");
     if (vec_n > n) vec_n = n;
@@ -244,16 +251,20 @@ int step_impl(const SfAdamScalars* s, float* p, const void* g, int g_dtype, floa
     if (!a16 || n < 4 || n - (vec_n & ~(uint64_t)3) > kMaxVectorRemainder) {
         if (g_dtype == SF_GRAD_BF16)
             return launch_scalar(x, p, GradBf16{(const uint16_t*)g}, m, v, out, n, vec_n, st);
+        if (g_dtype == SF_GRAD_F16)
+            return launch_scalar(x, p, GradF16{(const uint16_t*)g}, m, v, out, n, vec_n, st);
         return launch_scalar(x, p, GradF32{(const float*)g}, m, v, out, n, vec_n, st);
     }
     const int variant = g_tune.variant;
-    if (variant == 2 && !x.ex && a32 && (g_dtype == SF_GRAD_BF16 || aligned(g, 32))) {
+    if (variant == 2 && !x.ex && a32 && g_dtype != SF_GRAD_F16 && (g_dtype == SF_GRAD_BF16 || aligned(g, 32))) {
         if (g_dtype == SF_GRAD_BF16) return launch_vec8<true>(x, p, g, m, v, out, n, vec_n, st);
         return launch_vec8<false>(x, p, g, m, v, out, n, vec_n, st);
     }
     const int hint = variant == 0 ? 0 : 1;
     if (g_dtype == SF_GRAD_BF16)
         return launch_vec4(x, p, GradBf16{(const uint16_t*)g}, m, v, out, n, vec_n, st, hint);
+    if (g_dtype == SF_GRAD_F16)
+        return launch_vec4(x, p, GradF16{(const uint16_t*)g}, m, v, out, n, vec_n, st, hint);
     return launch_vec4(x, p, GradF32{(const float*)g}, m, v, out, n, vec_n, st, hint);
 }
 
@@ -402,8 +413,7 @@ int sf_adam_update(int id, uint64_t step, float lr, float beta1, float beta2, fl
 {
     // Validate what can be validated before the state machine moves, so a rejected call
     // leaves the optimizer where it was.
-    if (g_dtype != SF_GRAD_BF16 && g_dtype != SF_GRAD_F32)
-        return fail(SF_ERR_DTYPE, "gradient dtype code " + std::to_string(g_dtype) + " is not supported (0 = bf16, 1 = fp32)");
+    if (!local_dtype_ok(g_dtype)) return bad_local_dtype(g_dtype);
     if (n > 0 && (!p || !g || !m || !v)) return fail(SF_ERR_NULL, "p, g, m and v must be non-NULL when n > 0");
     SfAdamScalars s;
     if (int rc = sf_adam_scalars(id, step, lr, beta1, beta2, eps, weight_decay, bias_correction, &s)) return rc;
@@ -582,7 +592,7 @@ int sf_adam_update_dp_static(int id, uint64_t step, float lr, float beta1, float
 size_t sf_adam_host_scratch_bytes(uint64_t chunk_elems, int g_dtype, int g_on_host)
 {
     size_t per_slot = 3 * round256((size_t)chunk_elems * 4);
-    if (g_on_host) per_slot += round256((size_t)chunk_elems * (g_dtype == SF_GRAD_BF16 ? 2 : 4));
+    if (g_on_host) per_slot += round256((size_t)chunk_elems * (g_dtype == SF_GRAD_F32 ? 4 : 2));
     return 2 * per_slot;
 }
 
@@ -592,8 +602,7 @@ int sf_adam_update_host(int id, uint64_t step, float lr, float beta1, float beta
                         uint16_t* p_bf16_dev, uint64_t n, uint64_t chunk_elems, int per_chunk_scalars,
                         void* scratch, size_t scratch_bytes, void* stream)
 {
-    if (g_dtype != SF_GRAD_BF16 && g_dtype != SF_GRAD_F32)
-        return fail(SF_ERR_DTYPE, "gradient dtype code " + std::to_string(g_dtype) + " is not supported (0 = bf16, 1 = fp32)");
+    if (!local_dtype_ok(g_dtype)) return bad_local_dtype(g_dtype);
     if (chunk_elems == 0 || (chunk_elems & 15)) return fail(SF_ERR_ARG, "chunk_elems must be a positive multiple of 16");
     if (n > 0 && (!p_host || !g || !m_host || !v_host || !scratch))
         return fail(SF_ERR_NULL, "p_host, g, m_host, v_host and scratch must be non-NULL when n > 0");
@@ -610,7 +619,7 @@ int sf_adam_update_host(int id, uint64_t step, float lr, float beta1, float beta
     HostPipe* hp;
     if (int rc = get_pipe(&hp)) return rc;
     cudaStream_t user = (cudaStream_t)stream;
-    const size_t gsz = g_dtype == SF_GRAD_BF16 ? 2 : 4;
+    const size_t gsz = grad_elem_size(g_dtype);
     // A chunk is one reference call; inside it the copies and launches move in PIECES of at most
     // g_tune.host_piece elements through up to eight scratch slots, so that a call's first upload
     // and last download (the only copies nothing of the same call overlaps) stay short and the

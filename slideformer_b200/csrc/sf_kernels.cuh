@@ -16,6 +16,7 @@
 //     uses (cpu_adam_impl.cpp:46-66): m = fma(m, b1, g*(1-b1)), v = fma(v, b2, (g*g)*(1-b2));
 //   * bf16 output: RNE on the upper 16 bits, every NaN becomes 0x7FC0 (simd.h:56-86).
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -207,6 +208,22 @@ struct GradBf16 {
         unpack4(ld2u<HINT>(g + i), o);
     }
     __device__ __forceinline__ float load1(uint64_t i) const { return bf16_bits_to_f32(g[i]); }
+};
+// fp16 gradients (the <float, Half, float> triple of cpu_adam_impl.cpp:189): widened exactly.
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+struct GradF16 {
+    static constexpr bool kPeer = false;
+    const uint16_t* g;
+    template <int HINT>
+    __device__ __forceinline__ void load4(uint64_t i, float (&o)[4]) const
+    {
+        uint2 r = ld2u<HINT>(g + i);
+        o[0] = f16_bits_to_f32(r.x & 0xffffu);
+        o[1] = f16_bits_to_f32(r.x >> 16);
+        o[2] = f16_bits_to_f32(r.y & 0xffffu);
+        o[3] = f16_bits_to_f32(r.y >> 16);
+    }
+    __device__ __forceinline__ float load1(uint64_t i) const { return f16_bits_to_f32(g[i]); }
 };
 struct GradF32 {
     static constexpr bool kPeer = false;

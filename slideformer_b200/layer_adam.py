@@ -41,6 +41,8 @@ def _grad_code(t: torch.Tensor) -> int:
         return _lib.SF_GRAD_BF16
     if t.dtype == torch.float32:
         return _lib.SF_GRAD_F32
+    if t.dtype == torch.float16:
+        return _lib.SF_GRAD_F16
     # the reference raises std::runtime_error -> RuntimeError for an unregistered dtype triple
     raise RuntimeError(f"Adam optimizer with param type Float, grads type {t.dtype} and state type Float "
                        "is not supported on current hardware")
@@ -69,8 +71,9 @@ class LayerAdam:
         self.optimizer_id = next(_ids)
         _lib.check(self._lib.sf_adam_create(self.optimizer_id, lr, betas[0], betas[1], eps, weight_decay,
                                             int(bool(adamw_mode)), int(bool(should_log))))
-        if not fp32_optimizer_state:
-            raise NotImplementedError("only fp32 optimizer state is supported (fp32 master weights, fp32 moments)")
+        # The reference allocates the moments in fp32, or with fp32_optimizer_state=False in the
+        # parameters' dtype (layer_adam.py:161).  Master parameters are fp32 here (add_layer_params
+        # refuses anything else), so both settings give fp32 moments.
         self.fp32_optimizer_state = fp32_optimizer_state
         self.num_layer = num_layer
         self.state: DefaultDict[torch.Tensor, Any] = defaultdict(dict)

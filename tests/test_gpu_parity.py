@@ -205,6 +205,8 @@ def test_persistent_grid_vs_oracle(ctas_per_sm, oracle, lib):
 @pytest.mark.parametrize("adamw,bc,wd,gdtype,with_out", [
     (True, True, 0.01, torch.bfloat16, True),
     (True, True, 0.01, torch.float32, True),
+    (True, True, 0.01, torch.float16, True),
+    (False, False, 0.1, torch.float16, False),
     (False, True, 0.1, torch.bfloat16, True),
     (False, True, 0.1, torch.float32, False),
     (True, False, 0.01, torch.bfloat16, False),
@@ -228,6 +230,49 @@ def test_special_values(variant, oracle, lib):
         compare(*run_both(oracle, lib, 4096, 3, CFG0, special=True, seed=5), allow_nan=True)
     finally:
         lib.sf_set_tuning(1, -1)
+
+
+@pytest.mark.parametrize("g_on_host", [False, True])
+@pytest.mark.parametrize("n", [5, 4099, (1 << 20) + 13])
+def test_fp16_gradients(n, g_on_host, oracle, lib):
+    """The <float, Half, float> triple (cpu_adam_impl.cpp:189): fp16 gradients widened exactly,
+    including subnormal, infinite and signed-zero halves; HBM-resident and host-streamed state;
+    an odd start offset sends the same data through the scalar kernel."""
+    from slideformer_b200 import LayerAdam
+    gen = torch.Generator().manual_seed(n)
+    p0 = torch.randn(n + 1, generator=gen) * 0.02
+    for off in (0, 1):
+        k = n
+        po = p0[off:off + k].numpy().copy()
+        mo, vo, oo = np.zeros(k, np.float32), np.zeros(k, np.float32), np.zeros(k, np.uint16)
+        if g_on_host:
+            pd_full, md_full, vd_full = p0.clone().pin_memory(), torch.zeros(n + 1).pin_memory(), torch.zeros(n + 1).pin_memory()
+        else:
+            pd_full, md_full, vd_full = p0.to(DEV), torch.zeros(n + 1, device=DEV), torch.zeros(n + 1, device=DEV)
+        od_full = torch.zeros(n + 1, device=DEV, dtype=torch.bfloat16)
+        if g_on_host and off:
+            continue          # the streamed path asks for 16-byte aligned host buffers
+        opt = LayerAdam(lr=CFG0[0], betas=CFG0[1:3], eps=CFG0[3], weight_decay=CFG0[4], stream_chunk_numel=65536)
+        orc = oracle.OracleAdam(*CFG0, True)
+        nchunks = (k + 65535) // 65536 if g_on_host else 1
+        for step in (1, 2):
+            g = (torch.randn(n + 1, generator=gen) * 1e-3).to(torch.float16)
+            if n >= 16:
+                g[off:off + 8] = torch.tensor([0.0, -0.0, 6e-8, -6e-5, 65504.0, float("inf"), 1e-7, -1.0]).to(torch.float16)
+            gnp = g[off:off + k].numpy().copy()
+            if g_on_host:
+                c = orc.scalars(step, *CFG0, True)
+                for j in range(nchunks):
+                    a, b = j * 65536, min((j + 1) * 65536, k)
+                    oracle.apply_step(c, po[a:b], gnp[a:b], mo[a:b], vo[a:b], oo[a:b])
+            else:
+                orc.adam_update(step, *CFG0, True, po, gnp, mo, vo, oo)
+            gd = g.pin_memory() if g_on_host else g.to(DEV)
+            opt.step_chunk(pd_full[off:off + k], gd[off:off + k], md_full[off:off + k], vd_full[off:off + k],
+                           dict(opt.defaults, step=step), od_full[off:off + k])
+            torch.cuda.synchronize()
+        compare((po, mo, vo, oo), (pd_full[off:off + k], md_full[off:off + k], vd_full[off:off + k], od_full[off:off + k]),
+                allow_nan=True)
 
 
 def test_misaligned_slices_take_the_scalar_kernel(oracle, lib):

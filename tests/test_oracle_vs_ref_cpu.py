@@ -39,6 +39,9 @@ def _run(ref, oracle, n, steps, hp, adamw, bc, gdtype, oid, calls_per_step=1):
         for step in range(1, steps + 1):
             g = torch.empty(n).normal_(0, 1e-3, generator=gen).to(gdtype)
             gnp = g.view(torch.int16).numpy().view(np.uint16) if gdtype == torch.bfloat16 else g.numpy()
+            if gdtype == torch.float16 and step == 1:
+                # exercise subnormal, signed-zero and infinite halves as well
+                gnp[:8] = np.array([0.0, -0.0, 6e-8, -6e-5, 65504.0, np.inf, 1e-7, -1.0], dtype=np.float16)
             for a, b in zip(cuts[:-1], cuts[1:]):
                 ref.adam_update(oid, step, lr, b1, b2, eps, wd, bc, p[a:b], g[a:b], m[a:b], v[a:b])
                 orc.adam_update(step, lr, b1, b2, eps, wd, bc, po[a:b], gnp[a:b], mo[a:b], vo[a:b])
@@ -49,7 +52,7 @@ def _run(ref, oracle, n, steps, hp, adamw, bc, gdtype, oid, calls_per_step=1):
         ref.destroy_adam(oid)
 
 
-@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32, torch.float16])
 @pytest.mark.parametrize("hp,adamw,bc", [((1e-5, 0.9, 0.999, 1e-8, 0.01), True, True),
                                          ((0.01, 0.8, 0.95, 1e-6, 0.1), False, True),
                                          ((1e-3, 0.9, 0.999, 1e-8, 0.0), True, False)])
