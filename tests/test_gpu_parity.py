@@ -400,7 +400,7 @@ def test_error_behaviour(lib):
     with pytest.raises(RuntimeError, match="contiguous"):
         opt.step_chunk(z[::2], z[:32].clone(), z[:32].clone(), z[:32].clone(), grp)
     with pytest.raises(RuntimeError, match="not supported"):
-        opt.step_chunk(z, z.to(torch.float16), z.clone(), z.clone(), grp)
+        opt.step_chunk(z, z.to(torch.float64), z.clone(), z.clone(), grp)
     with pytest.raises(RuntimeError, match="same number"):
         opt.step_chunk(z, z[:32].clone(), z.clone(), z.clone(), grp)
     with pytest.raises(RuntimeError, match="same CUDA device"):
