@@ -54,6 +54,8 @@ def _worker(rank, world, path, mode):
                 with torch.no_grad():
                     ref = again(input_ids=ids).logits.float()
                 assert torch.allclose(mine, ref, atol=2e-2, rtol=0), (mine - ref).abs().max().item()
+            eng.close()          # what the benchmark does between models: every buffer of the engine is dropped
+            assert all(u._params_flat is None and u._dp_state is None for u in eng.transformer_layers)
             dp.barrier()
             dp.close()
             return
@@ -114,6 +116,7 @@ def _worker(rank, world, path, mode):
                     assert np.array_equal(got, o[st.start:st.end]), (step, idx)
                 else:
                     assert np.array_equal(u._bf16_flat.view(torch.int16).cpu().numpy().view(np.uint16), o), (step, idx)
+        eng.close()
         dp.barrier()
         dp.close()
     finally:
