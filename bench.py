@@ -51,6 +51,7 @@ def ncu_traffic_bytes(units: int) -> float:
 
 
 _RESULT_FD = None
+T_START = time.perf_counter()
 
 
 def emit(line: str) -> None:
@@ -798,12 +799,54 @@ def main_b200(args):
         e2e = sh.e2e(K, chunk_numel=args.e2e_chunk, min_chunk_numel=args.e2e_min_chunk)
     sampler.stop()
 
+    # ---- the result line: what has been measured so far; the optional sections below add to it ----
+    line = {"metric": METRIC, "value": value, "unit": "Gparams/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": parallelism,
+                       "l2": "inputs (3.05 GB per step) exceed the 126 MB L2; gradient buffer rotates every step",
+                       "hyper": {"lr": HP["lr"], "betas": list(HP["betas"]), "eps": HP["eps"], "weight_decay": HP["weight_decay"]}},
+            "hbm_gbs": BYTES_PER_PARAM * value, "roofline": roofline, "cpu_baseline": None, "e2e": e2e,
+            "gpu_launches": int(launches), "clocks": sampler.summary(), "host": host_info}
+    line.update(extra)
+    extra = line          # the sections below keep writing into `extra`
+
     # ---- parity: a few more steps of the very objects that were timed, against the CPU oracle ----
     if not args.no_parity:
         parity = parity_single(dev, p, m, v, out, grads, n) if world == 1 else parity_sharded(sh, world, rank, dev)
         if parity["mismatches"]:
             raise SystemExit(f"parity check failed: {parity}")
         extra["parity"] = parity
+
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        r = run_cpu_arm(n, 8, 2, budget_s=20.0)
+        line["cpu_baseline"] = {"value": r["value"], "unit": "Gparams/s", "cores": r["cores"], "kind": r["kind"],
+                                "sample": r["sample"], "ms_per_step": r["ms_per_step"], "bf16_cast_ms": r["bf16_cast_ms"]}
+
+    # Everything from here on is additional reporting.  If one of these sections ever stalls (a
+    # collective that a peer never joins), the line measured so far is still printed: a timer on
+    # every rank ends the process at the deadline, rank 0 after emitting the line.
+    section = ["sweep"]
+    done = threading.Event()
+    emit_lock = threading.Lock()
+
+    def finish(truncated=None):
+        with emit_lock:
+            if done.is_set():
+                return
+            done.set()
+            if truncated:
+                line["truncated"] = f"deadline of {args.deadline:.0f} s reached during the '{truncated}' section"
+            if rank == 0:
+                emit(json.dumps(line))
+
+    def on_deadline():
+        finish(section[0])
+        os._exit(0)
+
+    timer = threading.Timer(max(1.0, args.deadline - (time.perf_counter() - T_START)), on_deadline)
+    timer.daemon = True
+    timer.start()
 
     # ---- the size sweep (kernel alone at N = 1; kernel and whole step when sharded) --------------
     if not args.no_sweep:
@@ -815,22 +858,18 @@ def main_b200(args):
         else:
             main_entry["nvlink_gbs_per_direction"] = roofline.get("achieved")
             extra["sweep"] = sweep_sharded(dev, world, args.dp_mode, main_entry)
-    if world > 1 and args.dp_mode == "fused" and not args.no_fast_mode:
-        extra["fast_mode"] = fast_mode_nvls(sh, dev, world, n)
+    section[0] = "nvlink"
     if world > 1 and not args.no_nvlink:
         extra["nvlink"] = measure_nvlink(sh.dp, dev)
         if roofline.get("bound") == "nvlink":
             both = extra["nvlink"]["store_and_load_all_gpus_gbs"]
             roofline["frac_of_measured_bidirectional_copy"] = roofline["achieved"] / both
-
-    cpu_baseline = None
-    if world == 1 and rank == 0 and not args.no_cpu_baseline:
-        r = run_cpu_arm(n, 8, 2, budget_s=20.0)
-        cpu_baseline = {"value": r["value"], "unit": "Gparams/s", "cores": r["cores"], "kind": r["kind"],
-                        "sample": r["sample"], "ms_per_step": r["ms_per_step"], "bf16_cast_ms": r["bf16_cast_ms"]}
+    section[0] = "fast_mode"
+    if world > 1 and args.dp_mode == "fused" and not args.no_fast_mode:
+        extra["fast_mode"] = fast_mode_nvls(sh, dev, world, n)
 
     # ---- fine-tune tokens/s with the same kernel inside the layer-sliding engine ------------------
-    finetune = None
+    section[0] = "finetune"
     if args.finetune != "none":
         import gc
         from slideformer_b200.finetune_bench import run_finetune
@@ -841,7 +880,6 @@ def main_b200(args):
             del sh
         gc.collect()
         torch.cuda.empty_cache()
-        # (model, batch per GPU, seq, timed steps, warm-up, state placement, window mode + meta build)
         # (model, batch per GPU, seq, timed steps, warm-up, state placement, window mode + meta build, HBM budget)
         jobs = [("gpt2-small", 8, 1024, 20, 5, "hbm", False, None), ("llama3.1-8b", 8, 1024, 4, 2, "hbm", False, None)]
         if world == 1:
@@ -852,31 +890,20 @@ def main_b200(args):
         if world == 8:
             # Llama-3.1-70B: state sharded 1/8, bf16 weights kept as slices and gathered per layer
             jobs.append(("llama3.1-70b", 4, 2048, 2, 1, "hbm", True, None))
-        finetune = []
+        line["finetune"] = []
         for name, fbatch, fseq, fsteps, fwarm, state_dev, window, budget in jobs:
+            section[0] = f"finetune {name} ({state_dev})"
             dp = None
             if world > 1:
                 from slideformer_b200.shared_data_parallel import SharedDataParallel
                 dp = SharedDataParallel(dtype=torch.bfloat16, exchange_slots=2)
-            finetune.append(run_finetune(name, fbatch, fseq, fsteps, fwarm, dev, world, rank, dp, state_device=state_dev,
-                                         weight_window=window, meta=window, hbm_state_budget_gb=budget))
+            line["finetune"].append(run_finetune(name, fbatch, fseq, fsteps, fwarm, dev, world, rank, dp, state_device=state_dev,
+                                                 weight_window=window, meta=window, hbm_state_budget_gb=budget))
             if dp is not None:
                 dp.close()
 
-    if rank == 0:
-        line = {"metric": METRIC, "value": value, "unit": "Gparams/s", "n_gpus": world, "steps": K, "warmup": W,
-                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic",
-                "config": {"workload": WORKLOAD, "parallelism": parallelism,
-                           "l2": "inputs (3.05 GB per step) exceed the 126 MB L2; gradient buffer rotates every step",
-                           "hyper": {"lr": HP["lr"], "betas": list(HP["betas"]), "eps": HP["eps"], "weight_decay": HP["weight_decay"]}},
-                "hbm_gbs": BYTES_PER_PARAM * value, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-                "gpu_launches": int(launches), "clocks": sampler.summary()}
-        line["host"] = host_info
-        line.update(extra)
-        if finetune is not None:
-            line["finetune"] = finetune
-        emit(json.dumps(line))
+    timer.cancel()
+    finish()
     if world > 1:
         dist.destroy_process_group()
     return 0
@@ -901,6 +928,9 @@ def main():
     ap.add_argument("--host-state", action="store_true", default=True)
     ap.add_argument("--no-host-state", dest="host_state", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--deadline", type=float, default=780.0,
+                    help="seconds after start at which the line measured so far is printed and the run ends, should an "
+                         "additional-reporting section (sweep, NVLink yardstick, NVLS variant, fine-tune) still be running")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of extra steps after the timed region")
     ap.add_argument("--no-sweep", action="store_true", help="skip the 1M / 16M / 218M / 1B size sweep")
     ap.add_argument("--no-nvlink", action="store_true", help="N > 1: skip the bare-copy NVLink measurement")
