@@ -26,9 +26,20 @@ def _parse_cpulist(text: str) -> set:
     return cpus
 
 
+_CPUS_OF_GPU: dict = {}
+
+
 def gpu_numa_cpus(device, sysfs: str = "/sys") -> Optional[set]:
     """CPUs of the NUMA node the GPU's PCIe slot hangs off, read from sysfs; None when the
-    machine does not say (single node, virtualised PCI topology, no NVML)."""
+    machine does not say (single node, virtualised PCI topology, no NVML).  Looked up once per
+    device."""
+    key = (str(device), sysfs)
+    if key not in _CPUS_OF_GPU:
+        _CPUS_OF_GPU[key] = _gpu_numa_cpus(device, sysfs)
+    return _CPUS_OF_GPU[key]
+
+
+def _gpu_numa_cpus(device, sysfs: str) -> Optional[set]:
     try:
         import pynvml
         pynvml.nvmlInit()
