@@ -582,18 +582,23 @@ def measure_nvlink(dp, dev, nbytes: int = 1 << 29, reps: int = 10) -> dict:
 
 
 
-def measure_pcie(dev, nbytes: int = 1 << 30, reps: int = 5) -> dict:
+def measure_pcie(dev, nbytes: int = 1 << 30, reps: int = 5, world: int = 1) -> dict:
     """Plain pinned-memory copy bandwidth of this box: each direction alone and both at once.
-    The denominators for the host-buffer paths (PCIe Gen5 x16: 63 GB/s per direction nominal)."""
+    The denominators for the host-buffer paths (PCIe Gen5 x16: 63 GB/s per direction nominal).
+    With world > 1 every rank copies at the same time and the slowest rank's rate is reported:
+    what the host gives each GPU when all of them move data at once."""
     import torch
-    h_in = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
-    h_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    from slideformer_b200.numa import pinned_empty
+    h_in = pinned_empty(nbytes, torch.uint8, dev)
+    h_out = pinned_empty(nbytes, torch.uint8, dev)
     d_in = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     d_out = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
     def timed(up: bool, down: bool) -> float:
         torch.cuda.synchronize(dev)
+        if world > 1:
+            torch.distributed.barrier()
         t0 = time.perf_counter()
         for _ in range(reps):
             if up:
@@ -607,9 +612,14 @@ def measure_pcie(dev, nbytes: int = 1 << 30, reps: int = 5) -> dict:
 
     timed(True, True)
     up, down, both = timed(True, False), timed(False, True), timed(True, True)
+    if world > 1:
+        t = torch.tensor([up, down, both], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        up, down, both = (float(x) for x in t)
     return {"h2d_gbs": nbytes / up / 1e9, "d2h_gbs": nbytes / down / 1e9,
             "bidirectional_each_gbs": nbytes / both / 1e9, "nominal_gen5_x16_gbs": 63.0,
-            "how": f"{nbytes >> 20} MiB pinned copies, {reps} repetitions, wall clock around a device synchronize"}
+            "how": f"{nbytes >> 20} MiB pinned copies, {reps} repetitions, wall clock around a device synchronize"
+                   + (f"; all {world} GPUs copying at once, slowest rank" if world > 1 else "")}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -797,6 +807,8 @@ def main_b200(args):
             del ph, mh, vh
     else:
         e2e = sh.e2e(K, chunk_numel=args.e2e_chunk, min_chunk_numel=args.e2e_min_chunk)
+        extra["pcie"] = measure_pcie(dev, nbytes=1 << 29, world=world)
+        e2e["h2d_fraction_of_concurrent_pcie"] = e2e["h2d_gbs_per_gpu"] / extra["pcie"]["h2d_gbs"]
     sampler.stop()
 
     # ---- the result line: what has been measured so far; the optional sections below add to it ----
